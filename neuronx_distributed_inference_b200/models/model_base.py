@@ -131,6 +131,57 @@ class ParallelDecoderLayer(nn.Module):
         return x, hn
 
 
+class ConvPreNormDecoderLayer(nn.Module):
+    """Pre-norm block on an fp32 residual stream whose sublayers read a short causal convolution over time of the normalised stream:
+    ``h = norm1(x)``, ``x <- x + mixer(h + conv1(h))``, then, when the block has an MLP, ``h = norm2(x)``, ``x <- x + mlp(h + conv2(h))``.
+    ``conv*_weight`` are depthwise weights ``[width, taps]`` (``taps = 0``: plain pre-norm sublayers); the ``taps - 1`` stream rows before a
+    portion are carried per sequence in a state line (fp32), one line set per RUN of the block (``cache_index``: a block may run
+    several times per forward, each run with caches and carried rows of its own).  Sum, norm and convolution are ONE kernel
+    (``ops.stream_norm_conv``); the output of the block's last sublayer is handed on unadded (``pending``) so that the next block's
+    first kernel does the sum — ``forward`` takes and returns ``(x, pending)``; ``extra`` is one more fp32 term of that first sum."""
+    mlp_is_moe = False
+
+    def __init__(self, mixer: nn.Module, mlp: Optional[nn.Module], norm1: nn.Module, norm2: Optional[nn.Module], width: int, taps: int,
+                 layer_idx: int = 0, device=None):
+        super().__init__()
+        self.mixer, self.mlp, self.norm1, self.norm2, self.layer_idx = mixer, mlp, norm1, norm2, layer_idx
+        conv = lambda: nn.Parameter(torch.zeros(width, taps, dtype=torch.float32, device=device), requires_grad=False)      # noqa: E731
+        self.conv1_weight = conv() if taps else None
+        self.conv2_weight = conv() if taps and mlp is not None else None
+
+    def _state(self, which: int, run) -> str:
+        return f"stream_conv{self.layer_idx}.{which}.run{run}"
+
+    def state_specs(self, run=0):
+        specs = {}
+        for which, w in ((1, self.conv1_weight), (2, self.conv2_weight)):
+            if w is not None and w.shape[1] > 1:
+                specs[self._state(which, run)] = ((w.shape[1] - 1, w.shape[0]), torch.float32)
+        mixer_specs = getattr(self.mixer, "state_specs", None)
+        if mixer_specs is not None:
+            specs.update(mixer_specs(run))
+        return specs
+
+    def _read(self, x, adds, norm, conv, which, run, meta, kv_mgr):
+        ex = meta.extras
+        carried = conv is not None and conv.shape[1] > 1
+        st = kv_mgr.states.tensor(self._state(which, run)) if carried else None
+        s, h = ops.stream_norm_conv(x, adds, norm.weight, conv, st, ex["state_lines"], ex["ctx_len"], ex["q_len"], norm.variance_epsilon,
+                                    ex["act_dtype"])
+        if carried:
+            ops.short_conv_update(s, st, ex["state_lines"], ex["ctx_len"], ex["q_len"])
+        return s, h
+
+    def forward(self, x, pending, meta, kv_mgr, cache_index=None, extra=None):
+        run = self.layer_idx if cache_index is None else cache_index
+        x, h = self._read(x, (pending, extra), self.norm1, self.conv1_weight, 1, run, meta, kv_mgr)
+        y = self.mixer(h, meta, kv_mgr, cache_index=run)
+        if self.mlp is not None:
+            x, h = self._read(x, (y,), self.norm2, self.conv2_weight, 2, run, meta, kv_mgr)
+            y = self.mlp(h)
+        return x, y
+
+
 class NeuronBaseModel(nn.Module):
     """Generic causal decoder.  Subclass hooks: ``setup_attr_for_model(config)`` (set
     ``tp_degree, hidden_size, num_attention_heads, num_key_value_heads, max_batch_size,

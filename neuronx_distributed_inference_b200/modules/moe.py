@@ -32,11 +32,18 @@ class RouterTopK(nn.Module):
 
     def __init__(self, num_experts: int, top_k: int, hidden_size: int, dtype=torch.float32, act_fn: str = "softmax",
                  bias: bool = False, normalize_top_k_affinities: bool = True, apply_act_fn_over_topk: bool = False,
-                 device=None, renorm_eps: Optional[float] = None):
+                 device=None, renorm_eps: Optional[float] = None, correction: bool = False, groups=None, scale: float = 1.0):
         """``renorm_eps``: the chosen scores are divided by ``their sum + renorm_eps`` whatever ``act_fn`` is (sigmoid scores that are
-        renormalised over the chosen experts); ``None`` keeps the softmax-only ``normalize_top_k_affinities`` rule."""
+        renormalised over the chosen experts); ``None`` keeps the softmax-only ``normalize_top_k_affinities`` rule.
+        ``correction``: a per-expert term (``score_correction`` [E] fp32) is added to the scores for the CHOICE of experts only;
+        ``groups = (count, keep)``: only experts of the ``keep`` best of ``count`` equal groups of neighbours can be chosen (a group is
+        as good as its best corrected score); ``scale`` multiplies the weights.  ``num_experts`` counts every router output,
+        identity experts of :class:`MoE` included."""
         super().__init__()
         self.renorm_eps = renorm_eps
+        self.groups = None if not groups or int(groups[0]) <= 1 else (int(groups[0]), int(groups[1]))
+        self.scale = float(scale)
+        self.score_correction = nn.Parameter(torch.zeros(num_experts, dtype=torch.float32, device=device), requires_grad=False) if correction else None
         self.num_experts, self.top_k, self.act_fn = num_experts, top_k, act_fn
         self.normalize = normalize_top_k_affinities
         self.act_over_topk = apply_act_fn_over_topk
@@ -46,16 +53,18 @@ class RouterTopK(nn.Module):
         self.compute_dtype = torch.float32      # router_config["dtype"] (reference RouterConfig): precision of the router GEMM
 
     def forward(self, x: torch.Tensor):
+        extra = (self.score_correction, self.groups, self.scale)
         if self.compute_dtype != torch.float32:
             cd = self.compute_dtype
             logits = nn.functional.linear(x.to(cd), self.linear_router.weight.to(cd),
                                           None if self.linear_router.bias is None else self.linear_router.bias.to(cd)).float()
-            w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
+            w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps, *extra)
             return logits, w, idx
         if self.linear_router.bias is None:
-            return ops.router_topk(x, self.linear_router.weight, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
+            return ops.router_topk(x, self.linear_router.weight, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps,
+                                   *extra)
         logits = nn.functional.linear(x.float(), self.linear_router.weight, self.linear_router.bias)
-        w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps)
+        w, idx = ops.moe_route(logits, self.top_k, self.act_fn, self.normalize, self.act_over_topk, self.renorm_eps, *extra)
         return logits, w, idx
 
 
@@ -123,8 +132,11 @@ class MoE(nn.Module):
 
     def __init__(self, router: RouterTopK, expert_mlps: ExpertMLPs, shared_experts: Optional[nn.Module] = None,
                  return_router_logits: bool = False, return_expert_index: bool = False,
-                 early_affinity_modulation: bool = False):
+                 early_affinity_modulation: bool = False, identity_experts: int = 0):
+        """``identity_experts``: the LAST that many router outputs have no expert behind them: a token routed there gets its own input
+        back, times the weight (``expert_mlps`` holds the ``router.num_experts - identity_experts`` real experts)."""
         super().__init__()
+        self.identity_experts = int(identity_experts)
         self.router = router
         self.expert_mlps = expert_mlps
         self.shared_experts = shared_experts
@@ -149,6 +161,8 @@ class MoE(nn.Module):
             y = self.expert_mlps(x2, w.to(torch.float32), idx, scale_input=True)   # Llama-4: y = sum_j expert_j(x * w_j)
         else:
             y = self.expert_mlps(x2, w.to(torch.float32), idx)
+        if self.identity_experts:
+            y = ops.identity_expert_add(y, x2, w, idx, self.router.num_experts - self.identity_experts)
         if self.shared_experts is not None:
             sh = self.shared_experts(x2, reduce=False)
             if self.shared_expert_gate is not None:    # same scalar on every rank: commutes with the TP reduction below

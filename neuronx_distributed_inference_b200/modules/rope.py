@@ -17,9 +17,10 @@ def _yarn_find_dim(num_rot, dim, base, max_pos):
     return (dim * math.log(max_pos / (num_rot * 2 * math.pi))) / (2 * math.log(base))
 
 
-def compute_inv_freq(dim: int, base: float, scaling: Optional[dict] = None, max_pos: int = 8192):
-    """-> (inv_freq [dim/2] fp32, attention scale factor applied to cos/sin)."""
-    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+def compute_inv_freq(dim: int, base: float, scaling: Optional[dict] = None, max_pos: int = 8192, dtype=torch.float32):
+    """-> (inv_freq [dim/2] in ``dtype``, attention scale factor applied to cos/sin).  ``dtype=torch.float64`` for callers that form
+    the angles in fp64 (ragged rows at far positions)."""
+    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=dtype) / dim))
     mscale = 1.0
     if not scaling:
         return inv, mscale
@@ -52,7 +53,7 @@ def compute_inv_freq(dim: int, base: float, scaling: Optional[dict] = None, max_
         if scaling.get("truncate", True) is False:
             lo = max(_yarn_find_dim(beta_fast, dim, base, old), 0)
             hi = min(_yarn_find_dim(beta_slow, dim, base, old), dim - 1)
-        ramp = ((torch.arange(dim // 2, dtype=torch.float32) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
+        ramp = ((torch.arange(dim // 2, dtype=dtype) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
         extrap_mask = 1 - ramp
         inv = inv / factor * (1 - extrap_mask) + inv * extrap_mask
         ms = scaling.get("mscale", 1.0)

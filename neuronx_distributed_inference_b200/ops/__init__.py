@@ -345,21 +345,37 @@ def sample(logits, top_k, top_p, temperature, rand=None, global_topk: int = 256)
     return ref.sample(logits, top_k, top_p, temperature, rand, global_topk)
 
 
-def moe_route(router_logits, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None):
-    return ref.moe_route(router_logits, top_k, act, normalize, act_over_topk, renorm_eps)
+def moe_route(router_logits, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None, correction=None, groups=None,
+              scale=1.0):
+    return ref.moe_route(router_logits, top_k, act, normalize, act_over_topk, renorm_eps, correction, groups, scale)
 
 
-def router_topk(x, weight, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None):
-    """fp32 router: ``logits = x W^T`` (W fp32), then :func:`moe_route`.  Sigmoid routers run as two kernels on CUDA (fp32 products
-    with the rows in shared memory; selection and renormalisation, one warp per token) instead of a cast, a library GEMM and six
+def router_topk(x, weight, top_k, act="softmax", normalize=True, act_over_topk=False, renorm_eps=None, correction=None, groups=None,
+                scale=1.0):
+    """fp32 router: ``logits = x W^T`` (W fp32), then :func:`moe_route`.  Sigmoid routers, and softmax routers that are not
+    renormalised or that choose by corrected scores among kept groups, run as two kernels on CUDA (fp32 products with the rows in
+    shared memory; scores, group limit, selection and scaling, one warp per token) instead of a cast, a library GEMM and a chain of
     elementwise / sort launches.  -> (logits, weights [N, k] fp32, expert ids [N, k])."""
-    if (_mix_cuda(x) and act == "sigmoid" and not act_over_topk and weight.dtype == torch.float32 and x.dim() == 2 and top_k <= weight.shape[0]
-            and weight.shape[0] <= 512):
+    E = weight.shape[0]
+    plain_softmax = act == "softmax" and (not normalize or correction is not None or groups is not None)
+    if (_mix_cuda(x) and (act == "sigmoid" or plain_softmax) and not act_over_topk and weight.dtype == torch.float32 and x.dim() == 2
+            and top_k <= E and E <= 512 and (groups is None or (E % int(groups[0]) == 0 and int(groups[1]) <= int(groups[0])))):
         stats["router_topk"] += 1
-        return _C().router_sigmoid_topk(x.contiguous(), weight.contiguous(), int(top_k), -1.0 if renorm_eps is None else float(renorm_eps))
+        count, keep = (int(groups[0]), int(groups[1])) if groups is not None else (1, 1)
+        return _C().router_topk(x.contiguous(), weight.contiguous(), int(top_k), -1.0 if renorm_eps is None else float(renorm_eps),
+                                act == "softmax", None if correction is None else correction.float().contiguous(), count, keep, float(scale))
     logits = torch.nn.functional.linear(x.float(), weight.float())
-    w, idx = moe_route(logits, top_k, act, normalize, act_over_topk, renorm_eps)
+    w, idx = moe_route(logits, top_k, act, normalize, act_over_topk, renorm_eps, correction, groups, scale)
     return logits, w, idx
+
+
+def identity_expert_add(y, x, topk_w, topk_i, num_experts: int):
+    """``y + x * (sum of the weights of the slots routed to identity experts, ids >= num_experts)`` (definition: ops/reference.py)."""
+    if _mix_cuda(y) and x.dtype == y.dtype and y.is_contiguous() and x.is_contiguous() and topk_i.shape[1] <= 64:
+        stats["identity_expert_add"] += 1
+        _C().identity_expert_add(y, x, topk_w.float().contiguous(), topk_i.to(torch.int32).contiguous(), int(num_experts))
+        return y
+    return ref.identity_expert_add(y, x, topk_w, topk_i, num_experts)
 
 
 def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_offset=0,
@@ -373,7 +389,16 @@ def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_off
         stats["moe_plain"] += 1
         tc = _MOE_GROUPED and x.dtype == torch.bfloat16 and x.shape[1] % 64 == 0 and w_down.shape[2] % 64 == 0 and N > GEMV_MAX_TOKENS
         return _C().moe_plain(x.contiguous(), w_gate_up, w_down, topk_w.float().contiguous(), topk_i.to(torch.int32).contiguous(),
-                              int(expert_offset), _MOE_PLAIN_ACTS[act], bool(tc))
+                              int(expert_offset), _MOE_PLAIN_ACTS[act], bool(tc), False)
+    bf16_shapes = x.dtype == torch.bfloat16 and x.shape[1] % 64 == 0 and w_down.shape[2] % 64 == 0
+    if (act == "silu_mul" and _mix_cuda(x) and not bf16_shapes and act_fn is None and gate_up_scale is None and down_scale is None
+            and gate_up_bias is None and down_bias is None and not scale_input and w_gate_up.dtype == x.dtype and w_down.dtype == x.dtype
+            and topk_i.dim() == 2 and topk_i.shape[1] <= 64 and w_gate_up.shape[0] <= 512 and w_gate_up.is_contiguous() and w_down.is_contiguous()):
+        # gated experts in fp32 or with sizes the tensor-core kernels do not take: the same permutation around the CUDA-core grouped
+        # GEMMs, the gate product as an elementwise pass between them
+        stats["moe_plain_gated"] += 1
+        return _C().moe_plain(x.contiguous(), w_gate_up, w_down, topk_w.float().contiguous(), topk_i.to(torch.int32).contiguous(),
+                              int(expert_offset), _UNARY_ACTS["silu"], False, True)
     if gate_up_scale is not None or down_scale is not None:
         # fp8 experts with dynamic activation quantisation asked for: W8A8 grouped GEMMs on the kind::f8f6f4 tensor-core path
         if (_use_cuda(x) and _MOE_GROUPED and _ACT_QUANT and N > GEMV_MAX_TOKENS and x.dtype == torch.bfloat16 and act in _MOE_ACTS
@@ -417,7 +442,7 @@ def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_off
 
 _MOE_GROUPED = os.environ.get("NXDI_B200_MOE_GROUPED", "1") == "1"
 _MOE_ACTS = {"silu_mul": 1, "gelu_tanh_mul": 2, "gelu_mul": 3, "gpt_oss_glu": 4}
-_UNARY_ACTS = {"relu": 1, "relu2": 2, "silu": 3, "gelu_tanh": 4}         # codes of csrc/seqmix.cu (unary_act, moe_plain, gated_act_mul)
+_UNARY_ACTS = {"relu": 1, "relu2": 2, "silu": 3, "gelu_tanh": 4, "sigmoid": 5}         # codes of csrc/seqmix.cu (unary_act, moe_plain, gated_act_mul)
 _MOE_PLAIN_ACTS = _UNARY_ACTS
 
 
@@ -493,21 +518,24 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
     if _mix_cuda(qkv) and qkv.stride(-1) == 1 and conv_w.shape[1] <= _MIX_MAX_TAPS and D % 2 == 0:
         stats["conv_qknorm_rope_append"] += 1
         return _C().conv_qknorm_rope_append(qkv, conv_w, state, _i32(slots), _i32(ctx_len), _i32(q_len), q_norm_w, k_norm_w, float(eps),
-                                            int(n_q), int(n_kv), int(D), int(Dv), cos.float().contiguous(), sin.float().contiguous(),
+                                            int(n_q), int(n_kv), int(D), int(Dv), None if cos is None else cos.float().contiguous(),
+                                            None if sin is None else sin.float().contiguous(),
                                             k_cache, v_cache, None if block_table is None else _i32(block_table))
     return ref.conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w, k_norm_w, eps, n_q, n_kv, D, Dv, cos, sin,
                                        k_cache, v_cache, block_table, out_dtype)
 
 
 def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate=None, sinks=None,
-                           gate_per_head: bool = False):
-    if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1) and v_cache.shape[-1] <= _MIX_MAX_VDIM:
+                           gate_per_head: bool = False, chunk=None, slopes=None, value_dim=None):
+    Dv = v_cache.shape[-1] if value_dim is None else int(value_dim)
+    if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1) and Dv <= _MIX_MAX_VDIM and not (chunk and window):
         stats["paged_window_attention"] += 1
         return _C().paged_window_attention(q.contiguous(), k_cache, v_cache, _i32(block_table), _i32(ctx_len), _i32(q_len), float(scale),
                                            float(softcap or 0.0), int(window or 0), int(keep_first or 0), gate,
-                                           None if sinks is None else sinks.float().contiguous(), bool(gate_per_head))
+                                           None if sinks is None else sinks.float().contiguous(), bool(gate_per_head), int(chunk or 0),
+                                           None if slopes is None else slopes.float().contiguous(), Dv)
     return ref.paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate, sinks,
-                                      gate_per_head)
+                                      gate_per_head, chunk, slopes, value_dim)
 
 
 def ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads, head_dim, n_state, n_groups):
@@ -556,13 +584,42 @@ def stream_add_rmsnorm(x, adds=(), normed=None, normed_weight=None, vec=None, we
     return ref.stream_add_rmsnorm(x, adds, normed, normed_weight, vec, weight, eps, lp_dtype, emit_stream_lp)
 
 
-def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len, emit_rows: bool = False):
-    """``emit_rows``: also return the normalised rows in token order ``[B, T, 1, rank]`` (zeros past ``q_len``)."""
-    if _mix_cuda(p) and p.stride(-1) == 1 and cache.dtype == p.dtype and cache.is_contiguous():
+def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len, emit_rows: bool = False,
+                       rot_dim: int = 0, cos=None, sin=None, q_rank: int = 0, q_weight=None):
+    """``emit_rows``: also return the cache rows in token order ``[B, T, 1, rank + rot_dim]`` (zeros past ``q_len``).  With ``q_rank``
+    the result is ``(rows, normalised query latent [B, T, q_rank])``."""
+    if _mix_cuda(p) and p.stride(-1) == 1 and cache.dtype == p.dtype and cache.is_contiguous() and rot_dim % 2 == 0:
         stats["latent_norm_append"] += 1
-        return _C().latent_norm_append(p, int(offset), int(rank), weight.float().contiguous(), float(eps), cache, _i32(block_table),
-                                       _i32(ctx_len), _i32(q_len), bool(emit_rows))
-    return ref.latent_norm_append(p, offset, rank, weight, eps, cache, block_table, ctx_len, q_len, emit_rows)
+        f32 = lambda t: None if t is None else t.float().contiguous()          # noqa: E731
+        rows, cq = _C().latent_norm_append(p, int(offset), int(rank), f32(weight), float(eps), cache, _i32(block_table),
+                                           _i32(ctx_len), _i32(q_len), bool(emit_rows), int(rot_dim), f32(cos), f32(sin), int(q_rank), f32(q_weight))
+        return (rows, cq) if q_rank else rows
+    return ref.latent_norm_append(p, offset, rank, weight, eps, cache, block_table, ctx_len, q_len, emit_rows, rot_dim, cos, sin, q_rank,
+                                  q_weight)
+
+
+def rope_half_tail(src, dst, rot_dim: int, cos, sin):
+    """Rotate-half rotation of the last ``rot_dim`` channels of every head of ``src`` into the last ``rot_dim`` channels of ``dst``."""
+    if _mix_cuda(src) and dst.dtype == src.dtype and src.is_contiguous() and dst.is_contiguous() and rot_dim % 2 == 0:
+        stats["rope_half_tail"] += 1
+        _C().rope_half_tail(src, dst, int(rot_dim), cos.float().contiguous(), sin.float().contiguous())
+        return dst
+    return ref.rope_half_tail(src, dst, rot_dim, cos, sin)
+
+
+def stream_norm_conv(x, adds, weight, conv_w, state, slots, ctx_len, q_len, eps: float, lp_dtype=None):
+    """fp32 residual stream update + norm + short causal convolution of the normalised rows, ONE kernel (definition: ops/reference.py)."""
+    adds = tuple(a for a in adds if a is not None)
+    taps = 1 if conv_w is None else conv_w.shape[1]
+    if (_use_cuda(x) and x.dtype == torch.float32 and len(adds) <= 2 and all(a.dtype in _MIX_DTYPES for a in adds) and taps <= _MIX_MAX_TAPS
+            and x.dim() == 3 and (state is None or state.dtype == torch.float32)):
+        stats["stream_norm_conv"] += 1
+        lp = lp_dtype == torch.bfloat16
+        a0, a1 = (adds + (None, None))[:2]
+        c = lambda t: None if t is None else t.contiguous()          # noqa: E731
+        return tuple(_C().stream_norm_conv(x.contiguous(), c(a0), c(a1), weight.float().contiguous(), None if conv_w is None else conv_w.float().contiguous(),
+                                           state, None if slots is None else _i32(slots), _i32(ctx_len), _i32(q_len), float(eps), lp))
+    return ref.stream_norm_conv(x, adds, weight, conv_w, state, slots, ctx_len, q_len, eps, lp_dtype)
 
 
 def head_gate_mul(x, gate):
@@ -580,14 +637,14 @@ def latent_prefill_on_tensor_cores(x, rank: int) -> bool:
     return _use_cuda(x) and x.dtype == torch.bfloat16 and rank == 128 and _ATTN_TC
 
 
-def gated_act_mul(gate, other, act: str = "gelu_tanh"):
+def gated_act_mul(gate, other, act: str = "gelu_tanh", act_on_other: bool = False):
     if _mix_cuda(gate) and other.dtype == gate.dtype and other.stride(-1) == 1 and gate.is_contiguous() and act in _UNARY_ACTS \
             and other.dim() == gate.dim() and other.shape == gate.shape:
         stats["gated_act_mul"] += 1
         C = gate.shape[-1]
         o2 = other if other.dim() == 2 else other.reshape(-1, C) if other.is_contiguous() else _rows_view(other)
-        return _C().gated_act_mul(gate.reshape(-1, C), o2, _UNARY_ACTS[act]).view(gate.shape)
-    return ref.gated_act_mul(gate, other, act)
+        return _C().gated_act_mul(gate.reshape(-1, C), o2, _UNARY_ACTS[act], bool(act_on_other)).view(gate.shape)
+    return ref.gated_act_mul(gate, other, act, act_on_other)
 
 
 def _rows_view(t):

@@ -76,6 +76,8 @@ def activation(y, act: str):
         return F.relu(y)
     if act == "relu2":
         return F.relu(y).square()
+    if act == "sigmoid":
+        return torch.sigmoid(y)
     raise ValueError(act)
 
 
@@ -266,10 +268,27 @@ def argmax(logits):
 
 
 def moe_route(router_logits, top_k: int, act: str = "softmax", normalize: bool = True,
-              act_over_topk: bool = False, renorm_eps=None):
+              act_over_topk: bool = False, renorm_eps=None, correction=None, groups=None, scale: float = 1.0):
     """-> (weights [N,top_k] fp32, expert ids [N,top_k]).  softmax-then-topk (Mixtral/DBRX/Qwen3),
-    sigmoid (Llama-4) or topk-then-softmax (GPT-OSS ``apply_act_fn_over_topk``)."""
+    sigmoid (Llama-4) or topk-then-softmax (GPT-OSS ``apply_act_fn_over_topk``).
+
+    ``correction`` [E] / ``groups`` (count, keep): the experts are CHOSEN by ``score + correction`` among the ``keep`` groups (of
+    ``count`` equal groups of neighbouring experts) whose largest corrected score is largest — every other expert counts as minus
+    infinity — while the weights are the uncorrected scores of the chosen ones; ``scale`` multiplies the weights."""
     x = router_logits.float()
+    if correction is not None or groups is not None:
+        p = torch.softmax(x, -1) if act == "softmax" else torch.sigmoid(x)
+        choice = p if correction is None else p + correction.float()
+        if groups is not None and groups[0] > 1:
+            count, keep = int(groups[0]), int(groups[1])
+            best = choice.view(x.shape[0], count, -1).max(-1).values
+            kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, torch.topk(best, keep, -1).indices, True)
+            choice = choice.masked_fill(~kept.repeat_interleave(x.shape[1] // count, 1), float("-inf"))
+        i = torch.topk(choice, top_k, -1).indices
+        w = p.gather(1, i)
+        if renorm_eps is not None:
+            w = w / (w.sum(-1, keepdim=True) + renorm_eps)
+        return w * scale, i
     if act_over_topk:
         v, i = torch.topk(x, top_k, -1)
         w = torch.softmax(v, -1) if act == "softmax" else torch.sigmoid(v)
@@ -280,7 +299,14 @@ def moe_route(router_logits, top_k: int, act: str = "softmax", normalize: bool =
         w = w / (w.sum(-1, keepdim=True) + renorm_eps)
     elif normalize and act == "softmax":
         w = w / w.sum(-1, keepdim=True)
-    return w, i
+    return (w if scale == 1.0 else w * scale), i
+
+
+def identity_expert_add(y, x, topk_w, topk_i, num_experts: int):
+    """Routed slots whose expert id is ``>= num_experts`` are identity experts (no weights: the expert's output is its input):
+    ``y + x * sum_j topk_w[:, j] [topk_i[:, j] >= num_experts]``, summed in fp32."""
+    coef = (topk_w.float() * (topk_i >= num_experts)).sum(-1, keepdim=True)
+    return (y.float() + x.float() * coef).to(y.dtype)
 
 
 def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act: str = "silu_mul", expert_offset: int = 0,
@@ -423,7 +449,8 @@ def rope_partial_interleaved(x, cos, sin):
 def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w, k_norm_w, eps: float, n_q: int, n_kv: int,
                             D: int, Dv: int, cos, sin, k_cache, v_cache, block_table, out_dtype=None):
     """Fused front half of a convolved-projection attention layer.  ``qkv`` [B, T, >= n_q*D + n_kv*(D+Dv)] holds the biased q | k | v
-    projections (``n_kv = 0``: queries only, for a layer that reads another layer's cache).  Steps: short causal convolution of every
+    projections (``n_kv = 0``: queries only, for a layer that reads another layer's cache; a norm weight of ``None`` skips that row
+    norm, ``cos = None`` skips the rotation).  Steps: short causal convolution of every
     channel (carried inputs in ``state``), RMS norm of the WHOLE q row and of the WHOLE k row (plain weights), rotation of the first
     ``2 * cos.shape[-1]`` channels of every q / k head, and the write of k (normed, rotated) and v (convolved only) into the paged
     caches ``[blocks, page, n_kv, D | Dv]`` at position ``ctx_len + t``.  Returns q [B, T, n_q, D]."""
@@ -432,12 +459,18 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
     C = Cq + Ck + Cv
     y = short_conv(qkv[..., :C], conv_w, None, state, slots, ctx_len, q_len)
     q = y[..., :Cq]
-    q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm_w.float()
-    q = rope_partial_interleaved(q.view(B, T, n_q, D), cos, sin)
+    if q_norm_w is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+    q = q.view(B, T, n_q, D)
+    if cos is not None:
+        q = rope_partial_interleaved(q, cos, sin)
     if n_kv:
         k = y[..., Cq:Cq + Ck]
-        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm_w.float()
-        k = rope_partial_interleaved(k.view(B, T, n_kv, D), cos, sin)
+        if k_norm_w is not None:
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm_w.float()
+        k = k.view(B, T, n_kv, D)
+        if cos is not None:
+            k = rope_partial_interleaved(k, cos, sin)
         v = y[..., Cq + Ck:].view(B, T, n_kv, Dv)
         page = k_cache.shape[1]
         t = torch.arange(T, device=qkv.device).view(1, T)
@@ -451,13 +484,19 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
 
 
 def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale: float, softcap: float, window: int,
-                           keep_first: int, gate=None, sinks=None, gate_per_head: bool = False):
+                           keep_first: int, gate=None, sinks=None, gate_per_head: bool = False, chunk=None, slopes=None, value_dim=None):
     """Soft-capped attention of ragged query rows over a paged cache that already holds their own keys.  Query at position
     ``p = ctx_len + t`` sees key ``j`` iff ``j <= p and (p - j < window or j < keep_first)``; ``window <= 0`` means unbounded.
     score = cap * tanh(scale * q.k / cap) (cap <= 0: none), softmax in fp32.  ``gate`` [B, T, Hq * Dv]: the output is multiplied by
     ``sigmoid(gate)`` (``gate_per_head``: gate [B, T, Hq], one factor per head).  ``sinks`` [Hq] fp32: ``exp(sinks[h])`` joins the
-    softmax denominator of head ``h`` (a slot without key or value, neither scaled nor capped).  q [B, T, Hq, D] -> [B, T, Hq * Dv]."""
+    softmax denominator of head ``h`` (a slot without key or value, neither scaled nor capped).  ``chunk`` > 0: key ``j`` is visible only
+    from positions of its own chunk, ``j // chunk == p // chunk`` (chunks count from position 0 of the sequence).  ``slopes`` [Hq] fp32:
+    ``slopes[h] * (p - j)`` is taken off the score of head ``h`` (after scale and cap).  ``value_dim``: the value of a key is the first
+    ``value_dim`` channels of the row in ``v_cache`` (latent caches whose key row is the latent followed by a rotated part).
+    q [B, T, Hq, D] -> [B, T, Hq * Dv]."""
     B, T, Hq, D = q.shape
+    if value_dim is not None:
+        v_cache = v_cache[..., :value_dim]
     page, G, Dv = v_cache.shape[1], v_cache.shape[2], v_cache.shape[3]
     bt = block_table.long().clamp_min(0)
     k = k_cache[bt].reshape(B, -1, G, D).float()
@@ -468,10 +507,14 @@ def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, sca
     see = j <= p
     if window and window > 0:
         see = see & ((p - j < window) | (j < keep_first))
+    if chunk and chunk > 0:
+        see = see & (torch.div(j, chunk, rounding_mode="floor") == torch.div(p, chunk, rounding_mode="floor"))
     rep = Hq // G
     s = torch.einsum("bthd,bshd->bhts", q.float(), k.repeat_interleave(rep, 2)) * scale
     if softcap and softcap > 0:
         s = softcap * torch.tanh(s / softcap)
+    if slopes is not None:
+        s = s - slopes.float().view(1, Hq, 1, 1) * (p - j).clamp_min(0).float().unsqueeze(1)
     s = s.masked_fill(~see.unsqueeze(1), float("-inf"))
     if sinks is not None:
         s = torch.cat([s, sinks.float().view(1, Hq, 1, 1).expand(B, Hq, T, 1)], -1)
@@ -558,25 +601,80 @@ def stream_add_rmsnorm(x, adds=(), normed=None, normed_weight=None, vec=None, we
     return s, (s.to(lp) if (emit_stream_lp and lp is not None) else None), h
 
 
-def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len, emit_rows: bool = False):
+def rotate_half_rows(x, cos, sin):
+    """x [..., R] with cos / sin broadcastable to [..., R / 2]: channel ``i`` pairs with ``i + R / 2``; the pair ``(u, v)`` becomes
+    ``(u cos - v sin, v cos + u sin)``.  fp32."""
+    half = x.shape[-1] // 2
+    u, v = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([u * cos - v * sin, v * cos + u * sin], -1)
+
+
+def latent_norm_append(p, offset: int, rank: int, weight, eps: float, cache, block_table, ctx_len, q_len, emit_rows: bool = False,
+                       rot_dim: int = 0, cos=None, sin=None, q_rank: int = 0, q_weight=None):
     """Channels ``[offset, offset + rank)`` of the projection rows ``p`` [B, T, C] are RMS-normalised (fp32, ``weight`` [rank]) and
-    written to the paged latent cache ``[blocks, page, 1, rank]`` at positions ``ctx_len + t`` for ``t < q_len``."""
+    written to the paged latent cache ``[blocks, page, 1, rank + rot_dim]`` at positions ``ctx_len + t`` for ``t < q_len``.
+
+    ``rot_dim`` > 0: the next ``rot_dim`` channels (not normalised) are one rotated key part shared by all heads; they are rotated in
+    the rotate-half layout with ``cos`` / ``sin`` [B, T, rot_dim / 2] and stored behind the latent in the same cache row.
+    ``q_rank`` > 0: channels ``[0, q_rank)`` are a query latent; its RMS norm times ``q_weight`` is returned as well
+    (``(rows, q_latent [B, T, q_rank])`` instead of ``rows``)."""
     B, T = p.shape[:2]
     page = cache.shape[1]
     c = p[..., offset:offset + rank].float()
     c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    if rot_dim:
+        c = torch.cat([c, rotate_half_rows(p[..., offset + rank:offset + rank + rot_dim], cos.float(), sin.float())], -1)
     pos = ctx_len.long().view(B, 1) + torch.arange(T, device=p.device).view(1, T)
     live = torch.arange(T, device=p.device).view(1, T) < q_len.long().view(B, 1)
     width = block_table.shape[1]
     blk = torch.gather(block_table.long(), 1, (pos // page).clamp(0, width - 1))
     flat = blk * page + pos % page
-    cache.view(-1, rank)[flat[live]] = c[live].to(cache.dtype)
-    if emit_rows:
-        return torch.where(live.unsqueeze(-1), c, torch.zeros_like(c)).to(cache.dtype).view(B, T, 1, rank)
+    cache.view(-1, rank + rot_dim)[flat[live]] = c[live].to(cache.dtype)
+    rows = torch.where(live.unsqueeze(-1), c, torch.zeros_like(c)).to(cache.dtype).view(B, T, 1, rank + rot_dim) if emit_rows else None
+    if q_rank:
+        cq = p[..., :q_rank].float()
+        cq = cq * torch.rsqrt(cq.pow(2).mean(-1, keepdim=True) + eps) * q_weight.float()
+        return rows, cq.to(p.dtype)
+    return rows
 
 
-def gated_act_mul(gate, other, act: str = "gelu_tanh"):
-    """``act(gate) * other`` in fp32, cast to the type of ``gate``; ``other`` may be a strided slice of a wider row."""
+def rope_half_tail(src, dst, rot_dim: int, cos, sin):
+    """The last ``rot_dim`` channels of every head of ``src`` [B, T, H, Ds] are rotated (rotate-half layout, ``cos`` / ``sin``
+    [B, T, rot_dim / 2], fp32) and written to the last ``rot_dim`` channels of the heads of ``dst`` [B, T, H, Dd]."""
+    dst[..., dst.shape[-1] - rot_dim:] = rotate_half_rows(src[..., src.shape[-1] - rot_dim:], cos.float().unsqueeze(2),
+                                                          sin.float().unsqueeze(2)).to(dst.dtype)
+    return dst
+
+
+def stream_norm_conv(x, adds, weight, conv_w, state, slots, ctx_len, q_len, eps: float, lp_dtype=None):
+    """Update of an fp32 residual stream, the norm that reads it and a short causal convolution over time of the normalised rows::
+
+        s_t = x_t + sum(adds_t)                                         (fp32)
+        h_t = rms_unit(s_t) * weight
+        y_t = h_t + sum_j conv_w[:, j] * h_(t - taps + 1 + j)           (zeros before the start of the sequence)
+
+    The rows ``s`` of the ``taps - 1`` positions before a portion come from line ``slots[b]`` of ``state`` [lines, taps - 1, W] fp32
+    (zero when ``ctx_len`` is 0) and are normalised like the new ones, so a result does not depend on where a prompt was cut.  The
+    state is NOT advanced (:func:`short_conv_update` on ``s`` does that).  ``conv_w = None``: no convolution.  Returns
+    ``(s fp32, y in lp_dtype (fp32 when None))``."""
+    s = x.float()
+    for a in adds:
+        if a is not None:
+            s = s + a.float()
+    unit = lambda v: v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight.float()       # noqa: E731
+    h = unit(s)
+    if conv_w is not None:
+        T, K = s.shape[1], conv_w.shape[1]
+        win = unit(_conv_window(s, state, slots, ctx_len)) if K > 1 else h
+        h = h + sum(win[:, j:j + T] * conv_w[:, j].float() for j in range(K))
+    return s, (h if lp_dtype in (None, torch.float32) else h.to(lp_dtype))
+
+
+def gated_act_mul(gate, other, act: str = "gelu_tanh", act_on_other: bool = False):
+    """``act(gate) * other`` in fp32, cast to the type of ``gate``; ``other`` may be a strided slice of a wider row.
+    ``act_on_other``: ``gate * act(other)`` instead (the activation goes on the strided operand)."""
+    if act_on_other:
+        return (gate.float() * activation(other.float(), act)).to(gate.dtype)
     return (activation(gate.float(), act) * other.float()).to(gate.dtype)
 
 

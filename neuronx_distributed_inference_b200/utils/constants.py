@@ -100,7 +100,8 @@ MODEL_TYPES.update({"wav2vec2": {"audio-frame-classification":
 MODEL_TYPES["fetodra"] = {"causal-lm": f"{_P}.fetodra.modeling_fetodra:NeuronFetodraForCausalLM"}
 # checkpoints that name their design by ``architecture`` instead of a Hugging Face ``model_type``
 MODEL_TYPES["sodudra"] = {"causal-lm": f"{_P}.sodudra.modeling_sodudra:NeuronSodudraForCausalLM"}
-ARCHITECTURES = {"Fetodra": "fetodra", "Sodudra": "sodudra"}
+MODEL_TYPES["tusipel"] = {"causal-lm": f"{_P}.tusipel.modeling_tusipel:NeuronTusipelForCausalLM"}
+ARCHITECTURES = {"Fetodra": "fetodra", "Sodudra": "sodudra", "Tusipel": "tusipel"}
 TASK_TYPES = ("causal-lm", "image-text-to-text", "speech-to-text", "text-to-image", "audio-frame-classification", "audio-text-to-text")
 
 
