@@ -34,6 +34,7 @@ __device__ __forceinline__ float act_apply(int act, float v) {
     case 2: { const float r = fmaxf(v, 0.f); return r * r; }
     case 3: return v / (1.f + expf(-v));
     case 4: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    case 5: return 1.f / (1.f + expf(-v));
     default: return v;
   }
 }
@@ -141,13 +142,23 @@ __device__ __forceinline__ float warp_dot(const T* a, const T* b, int n, int lan
 template <typename T>
 __global__ void __launch_bounds__(256) decode_up_kernel(const T* __restrict__ x, const T* __restrict__ w_up, const int* __restrict__ topk_i,
                                                         T* __restrict__ h, int entries, int k, int H, int I, int expert_offset, int e_local,
-                                                        int act) {
+                                                        int act, int gated) {
   const int lane = threadIdx.x & 31;
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= (long long)entries * I) return;
   const int ent = (int)(wid / I), i = (int)(wid % I);
   const int e = topk_i[ent] - expert_offset;
   if (e < 0 || e >= e_local) return;
+  if (gated) {      // w_up holds [gate; up] rows: act(gate . x) * (up . x), each product rounded to the activation type first
+    float g = warp_dot(x + (size_t)(ent / k) * H, w_up + ((size_t)e * 2 * I + i) * H, H, lane);
+    float u = warp_dot(x + (size_t)(ent / k) * H, w_up + ((size_t)e * 2 * I + I + i) * H, H, lane);
+    if constexpr (!std::is_same<T, float>::value) {
+      g = __bfloat162float(__float2bfloat16_rn(g));
+      u = __bfloat162float(__float2bfloat16_rn(u));
+    }
+    if (lane == 0) stx(h + (size_t)ent * I + i, act_apply(act, g) * u);
+    return;
+  }
   const float v = warp_dot(x + (size_t)(ent / k) * H, w_up + ((size_t)e * I + i) * H, H, lane);
   if (lane == 0) stx(h + (size_t)ent * I + i, act_apply(act, v));
 }
@@ -261,20 +272,35 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const T* __restrict_
 }
 
 __global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, float* __restrict__ topk_w, int* __restrict__ topk_i,
-                                                            int N, int E, int k, float renorm_eps) {
-  extern __shared__ float zsm[];                             // [8][E]
+                                                            int N, int E, int k, RouterSelect sel) {
+  extern __shared__ float zsm[];                             // per warp: [E] scores, [E] choice scores, [groups] group bests
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * 8 + warp;
   if (tok >= N) return;
-  float* z = zsm + warp * E;
-  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)tok * E + e];
+  const int G = sel.groups > 1 ? sel.groups : 0;
+  float* sc = zsm + (size_t)warp * (2 * E + G);
+  float* ch = sc + E;
+  float* gb = ch + E;
+  // scores: sigmoid, or softmax over all router outputs
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) { const float v = logits[(size_t)tok * E + e]; sc[e] = v; mx = fmaxf(mx, v); }
+  if (sel.softmax) {
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(sc[e] - mx); sc[e] = v; den += v; }
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) sc[e] = sc[e] / den;
+  } else {
+    for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+  }
+  for (int e = lane; e < E; e += 32) ch[e] = sc[e] + (sel.correction ? sel.correction[e] : 0.f);
   __syncwarp();
-  float sum = 0.f;
-  for (int j = 0; j < k; ++j) {
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = z[e];
+  // largest value of an array of n floats, lowest index on ties; every lane gets (value, index)
+  auto arg_max = [&](const float* a, int n, float& best, int& bi) {
+    best = -INFINITY;
+    bi = 0x7fffffff;
+    for (int e = lane; e < n; e += 32) {
+      const float v = a[e];
       if (v > best || (v == best && e < bi)) { best = v; bi = e; }
     }
 #pragma unroll
@@ -283,26 +309,63 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    const float sc = 1.f / (1.f + expf(-best));
-    sum += sc;
+    if (bi >= n) bi = 0;                                     // nothing left to choose from (or not a number): stay inside the array
+  };
+  if (G) {
+    // a group is as good as its best choice score; experts outside the `keep` best groups cannot be chosen
+    const int per = E / G;
+    for (int g = lane; g < G; g += 32) {
+      float m = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, ch[e]);
+      gb[g] = m;
+    }
+    __syncwarp();
+    for (int j = 0; j < sel.keep; ++j) {
+      float best;
+      int bg;
+      arg_max(gb, G, best, bg);
+      if (lane == 0) gb[bg] = NAN;                           // marks the group as kept; NaN never wins a later comparison
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!isnan(gb[e / per])) ch[e] = -INFINITY;            // group not kept
+    __syncwarp();
+  }
+  float sum = 0.f;
+  for (int j = 0; j < k; ++j) {
+    float best;
+    int bi;
+    arg_max(ch, E, best, bi);
+    const float w = sc[bi];
+    sum += w;
     if (lane == 0) {
-      topk_w[(size_t)tok * k + j] = sc;
+      topk_w[(size_t)tok * k + j] = w;
       topk_i[(size_t)tok * k + j] = bi;
-      z[bi] = -INFINITY;                                     // taken
+      ch[bi] = -INFINITY;                                    // taken
     }
     __syncwarp();
   }
-  if (renorm_eps >= 0.f) {
-    const float inv = 1.f / (sum + renorm_eps);
-    for (int j = lane; j < k; j += 32) topk_w[(size_t)tok * k + j] *= inv;
-  }
+  const float mul = (sel.renorm_eps >= 0.f ? 1.f / (sum + sel.renorm_eps) : 1.f) * sel.scale;
+  if (mul != 1.f)
+    for (int j = lane; j < k; j += 32) topk_w[(size_t)tok * k + j] *= mul;
+}
+
+// gated experts: h[r, i] = act(g[r, i]) * g[r, I + i] for the rows of used tiles of the [R, 2 I] first product
+template <typename T>
+__global__ void __launch_bounds__(256) gate_mul_rows_kernel(const T* __restrict__ gu, T* __restrict__ h, int I, int act,
+                                                            const int* __restrict__ tile_expert) {
+  const int r = blockIdx.x;
+  if (tile_expert[r >> 7] < 0) return;
+  const T* row = gu + (size_t)r * 2 * I;
+  for (int i = threadIdx.x; i < I; i += 256) stx(h + (size_t)r * I + i, act_apply(act, ldx(row + i)) * ldx(row + I + i));
 }
 
 }  // namespace
 
-void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
-                                float renorm_eps, bool lp, cudaStream_t st) {
+void router_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
+                        const RouterSelect& sel, bool lp, cudaStream_t st) {
   if (N <= 0) return;
+  if (sel.groups > 1 && (E % sel.groups != 0 || sel.keep < 1 || sel.keep > sel.groups)) throw std::runtime_error("router: groups must divide the experts");
   if (k > E) throw std::runtime_error("router: more experts chosen than there are");
   if (E > 4096) throw std::runtime_error("router: more than 4096 experts");
   const bool few = N <= 32;
@@ -318,7 +381,9 @@ void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, fl
   } else {
     if (few) go(router_logits_kernel<float, 1, 8>, (const float*)x); else go(router_logits_kernel<float, 4, 8>, (const float*)x);
   }
-  router_select_kernel<<<(N + 7) / 8, 256, sizeof(float) * 8 * (size_t)E, st>>>(logits, topk_w, topk_i, N, E, k, renorm_eps);
+  const size_t sel_smem = sizeof(float) * 8 * (size_t)(2 * E + (sel.groups > 1 ? sel.groups : 0));
+  if (sel_smem > 48 * 1024) cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem);
+  router_select_kernel<<<(N + 7) / 8, 256, sel_smem, st>>>(logits, topk_w, topk_i, N, E, k, sel);
 }
 
 void moe_plain_gather_launch(const void* x, const int* row_entry, const int* tile_expert, void* xp, int R, int H, int k, bool lp, cudaStream_t st) {
@@ -343,18 +408,24 @@ void moe_plain_combine_launch(const void* y, const float* topk_w, const int* pos
   else combine_kernel<float><<<N, 128, 0, st>>>((const float*)y, topk_w, pos, (float*)out, H, k);
 }
 
+void moe_plain_gate_mul_launch(const void* gu, void* h, int R, int I, int act, const int* tile_expert, bool lp, cudaStream_t st) {
+  if (R <= 0) return;
+  if (lp) gate_mul_rows_kernel<__nv_bfloat16><<<R, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, I, act, tile_expert);
+  else gate_mul_rows_kernel<float><<<R, 256, 0, st>>>((const float*)gu, (float*)h, I, act, tile_expert);
+}
+
 void moe_plain_decode_launch(const void* x, const void* w_up, const void* w_down, const float* topk_w, const int* topk_i, void* h, void* out,
-                             int N, int k, int H, int I, int expert_offset, int e_local, int act, bool lp, cudaStream_t st) {
+                             int N, int k, int H, int I, int expert_offset, int e_local, int act, bool gated, bool lp, cudaStream_t st) {
   if (N <= 0) return;
   const long long w1 = (long long)N * k * I, w2 = (long long)N * H;
   const unsigned g1 = (unsigned)((w1 + 7) / 8), g2 = (unsigned)((w2 + 7) / 8);
   if (lp) {
     decode_up_kernel<__nv_bfloat16><<<g1, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w_up, topk_i, (__nv_bfloat16*)h, N * k, k, H, I,
-                                                        expert_offset, e_local, act);
+                                                        expert_offset, e_local, act, (int)gated);
     decode_down_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>((const __nv_bfloat16*)h, (const __nv_bfloat16*)w_down, topk_w, topk_i, (__nv_bfloat16*)out, N, k,
                                                           H, I, expert_offset, e_local);
   } else {
-    decode_up_kernel<float><<<g1, 256, 0, st>>>((const float*)x, (const float*)w_up, topk_i, (float*)h, N * k, k, H, I, expert_offset, e_local, act);
+    decode_up_kernel<float><<<g1, 256, 0, st>>>((const float*)x, (const float*)w_up, topk_i, (float*)h, N * k, k, H, I, expert_offset, e_local, act, (int)gated);
     decode_down_kernel<float><<<g2, 256, 0, st>>>((const float*)h, (const float*)w_down, topk_w, topk_i, (float*)out, N, k, H, I, expert_offset,
                                                   e_local);
   }

@@ -126,8 +126,9 @@ __global__ void __launch_bounds__(256) conv_qknorm_rope_append_kernel(ConvQkPara
   }
   sq = block_sum(sq, red);
   sk = block_sum(sk, red);
-  const float rq = 1.f / sqrtf(sq / (float)Cq + p.eps);
-  const float rk = Ck ? 1.f / sqrtf(sk / (float)Ck + p.eps) : 0.f;
+  // a null norm weight: that row is not normalised
+  const float rq = p.q_norm_w ? 1.f / sqrtf(sq / (float)Cq + p.eps) : 1.f;
+  const float rk = (Ck && p.k_norm_w) ? 1.f / sqrtf(sk / (float)Ck + p.eps) : 1.f;
   const long long tok = (long long)b * p.T + t;
   const float* cs = p.cos + tok * (p.R / 2);
   const float* sn = p.sin + tok * (p.R / 2);
@@ -143,9 +144,9 @@ __global__ void __launch_bounds__(256) conv_qknorm_rope_append_kernel(ConvQkPara
     const float r = isq ? rq : rk;
     const float* nw = isq ? p.q_norm_w : p.k_norm_w;
     const int d = cc % p.D;
-    float self = buf[c] * r * nw[cc];
+    float self = buf[c] * r * (nw ? nw[cc] : 1.f);
     if (d < p.R) {
-      const float other = buf[c ^ 1] * r * nw[cc ^ 1];
+      const float other = buf[c ^ 1] * r * (nw ? nw[cc ^ 1] : 1.f);
       const float co = cs[d >> 1], si = sn[d >> 1];
       self = (d & 1) ? (self * co + other * si) : (self * co - other * si);
     }
@@ -195,8 +196,9 @@ __global__ void __launch_bounds__(256) conv_qknorm_rope_append_pair_kernel(ConvQ
   }
   sq = block_sum(sq, red);
   sk = block_sum(sk, red);
-  const float rq = 1.f / sqrtf(sq / (float)Cq + p.eps);
-  const float rk = Ck ? 1.f / sqrtf(sk / (float)Ck + p.eps) : 0.f;
+  // a null norm weight: that row is not normalised
+  const float rq = p.q_norm_w ? 1.f / sqrtf(sq / (float)Cq + p.eps) : 1.f;
+  const float rk = (Ck && p.k_norm_w) ? 1.f / sqrtf(sk / (float)Ck + p.eps) : 1.f;
   const long long tok = (long long)b * p.T + t;
   const float* cs = p.cos + tok * (p.R / 2);
   const float* sn = p.sin + tok * (p.R / 2);
@@ -212,7 +214,7 @@ __global__ void __launch_bounds__(256) conv_qknorm_rope_append_pair_kernel(ConvQ
     const float r = isq ? rq : rk;
     const float* nw = isq ? p.q_norm_w : p.k_norm_w;
     const int d = cc % p.D;
-    float a = buf[c] * r * nw[cc], bb = buf[c + 1] * r * nw[cc + 1];
+    float a = buf[c] * r * (nw ? nw[cc] : 1.f), bb = buf[c + 1] * r * (nw ? nw[cc + 1] : 1.f);
     if (d < p.R) {
       const float co = cs[d >> 1], si = sn[d >> 1];
       const float ra = a * co - bb * si, rb = bb * co + a * si;
@@ -274,9 +276,11 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
   for (int d = lane; d < D; d += 32) qs[d] = ldf(qrow + d) * p.scale;
   __syncwarp();
   const int pos = p.ctx_len[b] + t;
-  const int lo = p.window > 0 ? max(pos - p.window + 1, 0) : 0;
+  // visible keys: a window that ends at the query, or the query's chunk up to the query
+  const int lo = p.chunk > 0 ? (pos / p.chunk) * p.chunk : (p.window > 0 ? max(pos - p.window + 1, 0) : 0);
   const int nA = p.window > 0 ? min(p.keep_first, lo) : 0;       // kept first tokens that the window no longer covers
   const int n = nA + (pos - lo + 1);
+  const float slope = p.slopes ? p.slopes[h] : 0.f;
   const int* table = p.block_table + (long long)b * p.max_blocks;
   const bool kvec = ((D * (int)sizeof(T)) % 16) == 0;
   const T* kc = (const T*)p.k_cache;
@@ -287,7 +291,7 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
   // value rows whose byte size is 16 * 2^k (k <= 5) are read as 16-byte pieces, LPR lanes per row
   constexpr int VN = Vec<T>::N;
   const int LPR = Dv / VN;
-  const bool vvec = Dv % VN == 0 && LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0;
+  const bool vvec = Dv % VN == 0 && LPR >= 1 && LPR <= 32 && (LPR & (LPR - 1)) == 0 && (p.v_rs * (long long)sizeof(T)) % 16 == 0;
   const int sub = vvec ? lane / LPR : 0, piece = vvec ? lane % LPR : 0;
   float accv[VN];
 #pragma unroll
@@ -302,6 +306,7 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
       row = ((long long)table[j / p.page] * p.page + j % p.page) * p.G + g;
       s = dot_row(qs, kc + row * D, D, kvec);
       if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+      s -= slope * (float)(pos - j);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);          // m = -inf on the first chunk: exp(-inf) = 0
@@ -320,7 +325,7 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
         const float pw = __shfl_sync(0xffffffffu, pj, src & 31);
         const long long r = __shfl_sync(0xffffffffu, row, src & 31);
         if (src < cnt) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(vc + r * Dv + piece * VN);
+          const uint4 raw = *reinterpret_cast<const uint4*>(vc + r * p.v_rs + piece * VN);
           if constexpr (VN == 4) {
             accv[0] += pw * __uint_as_float(raw.x); accv[1] += pw * __uint_as_float(raw.y);
             accv[2] += pw * __uint_as_float(raw.z); accv[3] += pw * __uint_as_float(raw.w);
@@ -334,7 +339,7 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
       for (int jj = 0; jj < cnt; ++jj) {
         const float pw = __shfl_sync(0xffffffffu, pj, jj);
         const long long r = __shfl_sync(0xffffffffu, row, jj);
-        const T* vrow = vc + r * Dv;
+        const T* vrow = vc + r * p.v_rs;
 #pragma unroll
         for (int i = 0; i < ATT_VPL; ++i) {
           const int dv = lane + 32 * i;
@@ -413,9 +418,10 @@ constexpr int MMA_MT = 64, MMA_KT = 64;
 
 __device__ __forceinline__ float tanh_fast(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
 
-template <int D, int DV>
-__global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(WindowAttnParams p) {
-  constexpr int KS = D + 8, VS = DV + 8, STAGE = MMA_KT * (KS + VS);
+// VPREFIX: the value of a key is the first DV channels of its key row (latent caches): the key tile in shared memory serves both products.
+template <int D, int DV, bool VPREFIX>
+__global__ void __launch_bounds__(128, (D + DV <= 256) ? 3 : 2) paged_window_attention_mma_kernel(WindowAttnParams p) {
+  constexpr int KS = D + 8, VS = VPREFIX ? KS : DV + 8, STAGE = MMA_KT * (VPREFIX ? KS : KS + VS);
   extern __shared__ __align__(16) unsigned char mma_smem[];       // two stages of [64][KS] keys + [64][VS] values
   __nv_bfloat16* stage0 = reinterpret_cast<__nv_bfloat16*>(mma_smem);
   const int h = blockIdx.y, b = blockIdx.z, t0 = blockIdx.x * MMA_MT;
@@ -442,8 +448,9 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int p_first = ctx + t0, p_last = ctx + min(t0 + MMA_MT, qn) - 1;
-  const int lo = p.window > 0 ? max(p_first - p.window + 1, 0) : 0;
+  const int lo = p.chunk > 0 ? (p_first / p.chunk) * p.chunk : (p.window > 0 ? max(p_first - p.window + 1, 0) : 0);
   const int nA = p.window > 0 ? min(p.keep_first, lo) : 0;
+  const float slope = p.slopes ? p.slopes[h] : 0.f;
   const int* table = p.block_table + (long long)b * p.max_blocks;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)p.k_cache;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)p.v_cache;
@@ -461,10 +468,10 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
     int j0, end;
     tile_range(i, j0, end);
     __nv_bfloat16* Kd = stage0 + (i & 1) * STAGE;
-    __nv_bfloat16* Vd = Kd + MMA_KT * KS;
+    __nv_bfloat16* Vd = VPREFIX ? Kd : Kd + MMA_KT * KS;
     // every copy is independent of the others (addresses from the block table, no carried state), so all of them are in flight at
     // once; pages of 2^k tokens (the usual case) are located with a shift and a mask instead of a division
-    auto copy_rows = [&](const __nv_bfloat16* cache, __nv_bfloat16* dst0, auto Wc, auto LDc) {
+    auto copy_rows = [&](const __nv_bfloat16* cache, long long rs, __nv_bfloat16* dst0, auto Wc, auto LDc) {
       constexpr int W = decltype(Wc)::value, LD = decltype(LDc)::value, cpr = W / 8;
 #pragma unroll
       for (int k = 0; k < MMA_KT * cpr / 128; ++k) {
@@ -473,11 +480,11 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
         const long long row = ((long long)table[pi] * p.page + po) * p.G + g;
         const uint32_t dst = (uint32_t)__cvta_generic_to_shared(dst0 + r * LD + ch * 8);
         const int nbytes = j < end ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(cache + row * W + ch * 8), "r"(nbytes));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(cache + row * rs + ch * 8), "r"(nbytes));
       }
     };
-    copy_rows(kc, Kd, std::integral_constant<int, D>{}, std::integral_constant<int, KS>{});
-    copy_rows(vc, Vd, std::integral_constant<int, DV>{}, std::integral_constant<int, VS>{});
+    copy_rows(kc, (long long)D, Kd, std::integral_constant<int, D>{}, std::integral_constant<int, KS>{});
+    if constexpr (!VPREFIX) copy_rows(vc, p.v_rs, Vd, std::integral_constant<int, DV>{}, std::integral_constant<int, VS>{});
     asm volatile("cp.async.commit_group;");
   };
   load_tile(0);
@@ -492,7 +499,7 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
     int j0, end;
     tile_range(i, j0, end);
     const __nv_bfloat16* Ks = stage0 + (i & 1) * STAGE;
-    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(Ks + MMA_KT * KS);
+    const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(VPREFIX ? Ks : Ks + MMA_KT * KS);
     {
       float sc[MMA_KT / 8][4];
 #pragma unroll
@@ -507,7 +514,8 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
         }
       // a tile that every row of this warp sees completely needs no mask
       const bool full = j0 + MMA_KT <= end && j0 + MMA_KT - 1 <= warp_pos_lo &&
-                        (p.window <= 0 || warp_pos_hi - j0 < p.window || j0 + MMA_KT <= p.keep_first);
+                        (p.window <= 0 || warp_pos_hi - j0 < p.window || j0 + MMA_KT <= p.keep_first) &&
+                        (p.chunk <= 0 || j0 / p.chunk == warp_pos_hi / p.chunk);
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
       for (int nt = 0; nt < MMA_KT / 8; ++nt)
@@ -515,10 +523,12 @@ __global__ void __launch_bounds__(128, 3) paged_window_attention_mma_kernel(Wind
         for (int e = 0; e < 4; ++e) {
           float v = sc[nt][e] * p.scale;
           if (p.softcap > 0.f) v = p.softcap * tanh_fast(v * inv_cap);
+          const int j = j0 + nt * 8 + tig * 2 + (e & 1);
+          const int pos = (e < 2) ? pos0 : pos1;
+          v -= slope * (float)(pos - j);
           if (!full) {
-            const int j = j0 + nt * 8 + tig * 2 + (e & 1);
-            const int pos = (e < 2) ? pos0 : pos1;
-            const bool see = j < end && j <= pos && (p.window <= 0 || pos - j < p.window || j < p.keep_first);
+            const bool see = j < end && j <= pos && (p.window <= 0 || pos - j < p.window || j < p.keep_first) &&
+                             (p.chunk <= 0 || j / p.chunk == pos / p.chunk);
             v = see ? v : -INFINITY;
           }
           sc[nt][e] = v;
@@ -900,13 +910,23 @@ template <typename T>
 __global__ void __launch_bounds__(256) latent_norm_append_kernel(const T* __restrict__ p, long long p_sb, long long p_st, const float* __restrict__ w,
                                                                  T* __restrict__ cache, const int* __restrict__ block_table,
                                                                  const int* __restrict__ ctx_len, const int* __restrict__ q_len, int B, int Tn, int R,
-                                                                 int page, int max_blocks, float eps, T* __restrict__ rows_out) {
+                                                                 int page, int max_blocks, float eps, T* __restrict__ rows_out, int rot,
+                                                                 const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                                                 const T* __restrict__ q_in, int q_rank, const float* __restrict__ q_w,
+                                                                 T* __restrict__ q_out) {
   const int lane = threadIdx.x & 31;
   const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (tok >= (long long)B * Tn) return;
   const int b = (int)(tok / Tn), t = (int)(tok % Tn);
   if (t >= q_len[b]) return;
   const T* row = p + (long long)b * p_sb + (long long)t * p_st;
+  if (q_rank > 0) {      // the query latent of the same token: RMS norm into q_out
+    const T* qr = q_in + (long long)b * p_sb + (long long)t * p_st;
+    float qs = 0.f;
+    for (int c = lane; c < q_rank; c += 32) { const float x = ldf(qr + c); qs += x * x; }
+    const float rq = 1.f / sqrtf(warp_sum(qs) / (float)q_rank + eps);
+    for (int c = lane; c < q_rank; c += 32) stf(q_out + tok * q_rank + c, ldf(qr + c) * rq * q_w[c]);
+  }
   constexpr int KEEP = 8;                       // values per lane held in registers (rows up to 256 wide)
   float v[KEEP];
   float ss = 0.f;
@@ -919,8 +939,17 @@ __global__ void __launch_bounds__(256) latent_norm_append_kernel(const T* __rest
   for (int c = lane + 32 * KEEP; c < R; c += 32) { const float x = ldf(row + c); ss += x * x; }
   const float r = 1.f / sqrtf(warp_sum(ss) / (float)R + eps);
   const int pos = ctx_len[b] + t;
-  T* dst = cache + ((long long)block_table[(long long)b * max_blocks + pos / page] * page + pos % page) * R;
-  T* dst2 = rows_out ? rows_out + tok * R : nullptr;      // [B, T, R]: the same rows in token order
+  const int RW = R + rot;                                 // cache row: the latent, then the rotated key part
+  T* dst = cache + ((long long)block_table[(long long)b * max_blocks + pos / page] * page + pos % page) * RW;
+  T* dst2 = rows_out ? rows_out + tok * RW : nullptr;     // [B, T, RW]: the same rows in token order
+  for (int i = lane; i < rot / 2; i += 32) {              // rotate-half: channel i pairs with i + rot / 2
+    const float u = ldf(row + R + i), v = ldf(row + R + rot / 2 + i);
+    const float co = cosv[tok * (rot / 2) + i], si = sinv[tok * (rot / 2) + i];
+    const float a = u * co - v * si, bb = v * co + u * si;
+    stf(dst + R + i, a);
+    stf(dst + R + rot / 2 + i, bb);
+    if (dst2) { stf(dst2 + R + i, a); stf(dst2 + R + rot / 2 + i, bb); }
+  }
 #pragma unroll
   for (int i = 0; i < KEEP; ++i) {
     const int c = lane + 32 * i;
@@ -935,6 +964,89 @@ __global__ void __launch_bounds__(256) latent_norm_append_kernel(const T* __rest
     stf(dst + c, o);
     if (dst2) stf(dst2 + c, o);
   }
+}
+
+// dst[tok, h, Dd - rot + .] = rotate_half(src[tok, h, Ds - rot + .]); one thread per (token, head, pair)
+template <typename T>
+__global__ void __launch_bounds__(256) rope_half_tail_kernel(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ cosv,
+                                                             const float* __restrict__ sinv, long long n, int H, int Ds, int Dd, int rot) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const int half = rot / 2, i = (int)(idx % half);
+  const long long th = idx / half, tok = th / H;
+  const T* sr = src + th * Ds + (Ds - rot);
+  T* dr = dst + th * Dd + (Dd - rot);
+  const float u = ldf(sr + i), v = ldf(sr + half + i);
+  const float co = cosv[tok * half + i], si = sinv[tok * half + i];
+  stf(dr + i, u * co - v * si);
+  stf(dr + half + i, v * co + u * si);
+}
+
+// Stream update + norm + short convolution of the normalised rows.  Block = one token; window row j (j < K) is the stream row at
+// token index t - K + 1 + j: a new row (x + y1 + y2, formed here) or, before the portion, a carried row of the state line.  Pass 1
+// forms the K sums of squares, pass 2 re-reads the rows (cache hits) and writes the result.
+__device__ __forceinline__ float ld_any(const void* p, long long i, int lp) {
+  return lp ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i];
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) stream_norm_conv_kernel(StreamConvParams p) {
+  __shared__ float red[32];
+  const int b = blockIdx.y, t = blockIdx.x;
+  if (t >= p.q_len[b]) return;
+  const int W = p.W, K = p.K;
+  const bool has_ctx = p.ctx_len[b] > 0;
+  const long long base = (long long)b * p.T * W;
+  const float* sl = p.state ? p.state + (long long)p.lines[b] * (K - 1) * W : nullptr;
+  auto row_value = [&](int j, int c) -> float {
+    const int i = t - K + 1 + j;
+    if (i >= 0) {
+      const long long o = base + (long long)i * W + c;
+      float v = p.x[o];
+      if (p.y1) v += ld_any(p.y1, o, p.y1_lp);
+      if (p.y2) v += ld_any(p.y2, o, p.y2_lp);
+      return v;
+    }
+    return (has_ctx && sl) ? sl[(long long)(K - 1 + i) * W + c] : 0.f;
+  };
+  float ss[SEQMIX_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < SEQMIX_MAX_TAPS; ++j) ss[j] = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+#pragma unroll
+    for (int j = 0; j < SEQMIX_MAX_TAPS; ++j)
+      if (j < K) { const float v = row_value(j, c); ss[j] += v * v; }
+  }
+  float r[SEQMIX_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < SEQMIX_MAX_TAPS; ++j)
+    if (j < K) r[j] = 1.f / sqrtf(block_sum(ss[j], red) / (float)W + p.eps);
+  const long long o0 = base + (long long)t * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float wc = p.w[c];
+    float own = 0.f, acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < SEQMIX_MAX_TAPS; ++j)
+      if (j < K) {
+        const float v = row_value(j, c);
+        const float h = v * r[j] * wc;
+        if (p.cw) acc += p.cw[(long long)c * K + j] * h;
+        if (j == K - 1) { own = h; p.s[o0 + c] = v; }
+      }
+    stf((TO*)p.out + o0 + c, own + acc);
+  }
+}
+
+// y[tok, :] += x[tok, :] * (sum of the weights of the slots routed to ids >= num_experts); block = one token
+template <typename T>
+__global__ void __launch_bounds__(128) identity_expert_add_kernel(T* __restrict__ y, const T* __restrict__ x, const float* __restrict__ topk_w,
+                                                                  const int* __restrict__ topk_i, int H, int k, int num_experts) {
+  const long long tok = blockIdx.x;
+  float coef = 0.f;
+  for (int j = 0; j < k; ++j)
+    if (topk_i[tok * k + j] >= num_experts) coef += topk_w[tok * k + j];
+  if (coef == 0.f) return;
+  for (int c = threadIdx.x; c < H; c += 128) stf(y + tok * H + c, ldf(y + tok * H + c) + ldf(x + tok * H + c) * coef);
 }
 
 // x[row, h, :] *= sigmoid(gate[row, h]); 16 bytes per thread, D a multiple of the vector width
@@ -965,18 +1077,20 @@ __device__ __forceinline__ float unary_apply(int act, float v) {
     case 2: { const float r = fmaxf(v, 0.f); return r * r; }
     case 3: return v / (1.f + expf(-v));
     case 4: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    case 5: return 1.f / (1.f + expf(-v));
     default: return v;
   }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) gated_act_mul_kernel(const T* __restrict__ gate, const T* __restrict__ other, long long o_stride,
-                                                            T* __restrict__ out, long long rows, int C, int act) {
+__global__ void __launch_bounds__(256) gated_act_mul_kernel(const T* __restrict__ gate, long long g_stride, const T* __restrict__ other,
+                                                            long long o_stride, T* __restrict__ out, long long rows, int C, int act, int on_other) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= rows * C) return;
   const long long r = i / C;
   const int c = (int)(i % C);
-  stf(out + i, unary_apply(act, ldf(gate + i)) * ldf(other + r * o_stride + c));
+  const float g = ldf(gate + r * g_stride + c), o = ldf(other + r * o_stride + c);
+  stf(out + i, on_other ? g * unary_apply(act, o) : unary_apply(act, g) * o);
 }
 
 template <typename T>
@@ -988,11 +1102,11 @@ __global__ void __launch_bounds__(256) unary_act_kernel(const T* __restrict__ x,
 // 16 bytes per thread: `other` rows start at o_stride elements (a multiple of the vector width), C a multiple of it too
 template <typename T, bool MUL>
 __global__ void __launch_bounds__(256) act_vec_kernel(const T* __restrict__ x, const T* __restrict__ other, long long o_stride, T* __restrict__ out,
-                                                      long long nvec, int cvec, int act) {
+                                                      long long nvec, int cvec, int act, long long x_stride = 0, int on_other = 0) {
   constexpr int V = Vec<T>::N;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= nvec) return;
-  const uint4 a = *reinterpret_cast<const uint4*>(x + i * V);
+  const uint4 a = *reinterpret_cast<const uint4*>(MUL ? x + (i / cvec) * x_stride + (i % cvec) * V : x + i * V);
   uint4 b = make_uint4(0u, 0u, 0u, 0u);
   if constexpr (MUL) b = *reinterpret_cast<const uint4*>(other + (i / cvec) * o_stride + (i % cvec) * V);
   uint4 o;
@@ -1000,13 +1114,13 @@ __global__ void __launch_bounds__(256) act_vec_kernel(const T* __restrict__ x, c
     float f[4] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w)};
     const float m[4] = {__uint_as_float(b.x), __uint_as_float(b.y), __uint_as_float(b.z), __uint_as_float(b.w)};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) f[e] = unary_apply(act, f[e]) * (MUL ? m[e] : 1.f);
+    for (int e = 0; e < 4; ++e) f[e] = (MUL && on_other) ? f[e] * unary_apply(act, m[e]) : unary_apply(act, f[e]) * (MUL ? m[e] : 1.f);
     o = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
   } else {
     float f[8] = {bf16lo(a.x), bf16hi(a.x), bf16lo(a.y), bf16hi(a.y), bf16lo(a.z), bf16hi(a.z), bf16lo(a.w), bf16hi(a.w)};
     const float m[8] = {bf16lo(b.x), bf16hi(b.x), bf16lo(b.y), bf16hi(b.y), bf16lo(b.z), bf16hi(b.z), bf16lo(b.w), bf16hi(b.w)};
 #pragma unroll
-    for (int e = 0; e < 8; ++e) f[e] = unary_apply(act, f[e]) * (MUL ? m[e] : 1.f);
+    for (int e = 0; e < 8; ++e) f[e] = (MUL && on_other) ? f[e] * unary_apply(act, m[e]) : unary_apply(act, f[e]) * (MUL ? m[e] : 1.f);
     o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
   }
   *reinterpret_cast<uint4*>(out + i * V) = o;
@@ -1060,15 +1174,42 @@ void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, c
 
 void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, const float* w, void* cache, const int* block_table,
                                const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
-                               void* rows_out, cudaStream_t st) {
+                               void* rows_out, int rot, const float* cos, const float* sin, const void* q_in, int q_rank, const float* q_w,
+                               void* q_out, cudaStream_t st) {
   if (B <= 0 || T <= 0) return;
   const unsigned grid = (unsigned)(((long long)B * T + 7) / 8);
   if (lp)
     latent_norm_append_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)p, p_sb, p_st, w, (__nv_bfloat16*)cache, block_table, ctx_len,
-                                                                   q_len, B, T, R, page, max_blocks, eps, (__nv_bfloat16*)rows_out);
+                                                                   q_len, B, T, R, page, max_blocks, eps, (__nv_bfloat16*)rows_out, rot, cos, sin,
+                                                                   (const __nv_bfloat16*)q_in, q_rank, q_w, (__nv_bfloat16*)q_out);
   else
     latent_norm_append_kernel<float><<<grid, 256, 0, st>>>((const float*)p, p_sb, p_st, w, (float*)cache, block_table, ctx_len, q_len, B, T, R, page,
-                                                           max_blocks, eps, (float*)rows_out);
+                                                           max_blocks, eps, (float*)rows_out, rot, cos, sin, (const float*)q_in, q_rank, q_w,
+                                                           (float*)q_out);
+}
+
+void rope_half_tail_launch(const void* src, void* dst, const float* cos, const float* sin, long long tokens, int H, int Ds, int Dd, int rot, bool lp,
+                           cudaStream_t st) {
+  const long long n = tokens * H * (rot / 2);
+  if (n <= 0) return;
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (lp) rope_half_tail_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, cos, sin, n, H, Ds, Dd, rot);
+  else rope_half_tail_kernel<float><<<grid, 256, 0, st>>>((const float*)src, (float*)dst, cos, sin, n, H, Ds, Dd, rot);
+}
+
+void stream_norm_conv_launch(const StreamConvParams& p, bool out_lp, cudaStream_t st) {
+  if (p.B <= 0 || p.T <= 0) return;
+  dim3 grid(p.T, p.B);
+  const int threads = p.W >= 1024 ? 256 : 128;
+  if (out_lp) stream_norm_conv_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(p);
+  else stream_norm_conv_kernel<float><<<grid, threads, 0, st>>>(p);
+}
+
+void identity_expert_add_launch(void* y, const void* x, const float* topk_w, const int* topk_i, int N, int H, int k, int num_experts, bool lp,
+                                cudaStream_t st) {
+  if (N <= 0) return;
+  if (lp) identity_expert_add_kernel<__nv_bfloat16><<<N, 128, 0, st>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, topk_w, topk_i, H, k, num_experts);
+  else identity_expert_add_kernel<float><<<N, 128, 0, st>>>((float*)y, (const float*)x, topk_w, topk_i, H, k, num_experts);
 }
 
 void head_gate_mul_launch(void* x, const void* gate, long long g_stride, long long rows, int H, int D, bool lp, cudaStream_t st) {
@@ -1080,27 +1221,29 @@ void head_gate_mul_launch(void* x, const void* gate, long long g_stride, long lo
   else head_gate_mul_kernel<float><<<grid, 256, 0, st>>>((float*)x, (const float*)gate, g_stride, nvec, H, D / V);
 }
 
-void gated_act_mul_launch(const void* gate, const void* other, long long o_stride, void* out, long long rows, int C, int act, bool lp,
-                          cudaStream_t st) {
+void gated_act_mul_launch(const void* gate, long long g_stride, const void* other, long long o_stride, void* out, long long rows, int C, int act,
+                          bool on_other, bool lp, cudaStream_t st) {
   const long long n = rows * C;
   if (n <= 0) return;
   const int V = lp ? 8 : 4;
-  if (C % V == 0 && o_stride % V == 0 && (((uintptr_t)gate | (uintptr_t)other | (uintptr_t)out) & 15) == 0) {
+  if (C % V == 0 && o_stride % V == 0 && g_stride % V == 0 && (((uintptr_t)gate | (uintptr_t)other | (uintptr_t)out) & 15) == 0) {
     const long long nvec = n / V;
     const unsigned gv = (unsigned)((nvec + 255) / 256);
     if (lp)
       act_vec_kernel<__nv_bfloat16, true><<<gv, 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)other, o_stride, (__nv_bfloat16*)out, nvec,
-                                                              C / V, act);
+                                                              C / V, act, g_stride, (int)on_other);
     else
-      act_vec_kernel<float, true><<<gv, 256, 0, st>>>((const float*)gate, (const float*)other, o_stride, (float*)out, nvec, C / V, act);
+      act_vec_kernel<float, true><<<gv, 256, 0, st>>>((const float*)gate, (const float*)other, o_stride, (float*)out, nvec, C / V, act, g_stride,
+                                                      (int)on_other);
     return;
   }
   const unsigned grid = (unsigned)((n + 255) / 256);
   if (lp)
-    gated_act_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)other, o_stride, (__nv_bfloat16*)out,
-                                                              rows, C, act);
+    gated_act_mul_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)gate, g_stride, (const __nv_bfloat16*)other, o_stride,
+                                                              (__nv_bfloat16*)out, rows, C, act, (int)on_other);
   else
-    gated_act_mul_kernel<float><<<grid, 256, 0, st>>>((const float*)gate, (const float*)other, o_stride, (float*)out, rows, C, act);
+    gated_act_mul_kernel<float><<<grid, 256, 0, st>>>((const float*)gate, g_stride, (const float*)other, o_stride, (float*)out, rows, C, act,
+                                                      (int)on_other);
 }
 
 void unary_act_launch(const void* x, void* out, long long n, int act, bool lp, cudaStream_t st) {
@@ -1160,18 +1303,27 @@ void conv_qknorm_rope_append_launch(const ConvQkParams& p, bool lp, cudaStream_t
 void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStream_t st) {
   const long long nq = (long long)p.B * p.T * p.Hq;
   if (nq <= 0) return;
-  if (lp && p.T >= 16 && (p.D == 64 || p.D == 128) && (p.Dv == 64 || p.Dv == 128)) {
+  // values that are a prefix of the key rows of the same cache (latent rows with a rotated tail): one shared-memory tile serves both
+  const bool prefix = p.v_cache == p.k_cache && p.v_rs == p.D && p.G == 1;
+  const bool rows16 = (p.v_rs * 2) % 16 == 0;
+  if (lp && p.T >= 16 && rows16 && ((!prefix && (p.D == 64 || p.D == 128) && (p.Dv == 64 || p.Dv == 128)) ||
+                                    (prefix && ((p.D == 80 && p.Dv == 64) || (p.D == 192 && p.Dv == 128) || (p.D == p.Dv && (p.D == 64 || p.D == 128)))))) {
     // prompt portions in bf16: tensor-core kernel
     dim3 grid((p.T + MMA_MT - 1) / MMA_MT, p.Hq, p.B);
-    const size_t smem = 2 * (size_t)MMA_KT * (p.D + 8 + p.Dv + 8) * sizeof(__nv_bfloat16);
+    const size_t smem = 2 * (size_t)MMA_KT * (prefix ? p.D + 8 : p.D + 8 + p.Dv + 8) * sizeof(__nv_bfloat16);
     auto go = [&](auto kernel) {
       opt_in_smem(kernel, smem);
       kernel<<<grid, 128, smem, st>>>(p);
     };
-    if (p.D == 64 && p.Dv == 64) go(paged_window_attention_mma_kernel<64, 64>);
-    else if (p.D == 64) go(paged_window_attention_mma_kernel<64, 128>);
-    else if (p.Dv == 64) go(paged_window_attention_mma_kernel<128, 64>);
-    else go(paged_window_attention_mma_kernel<128, 128>);
+    if (prefix) {
+      if (p.D == 80) go(paged_window_attention_mma_kernel<80, 64, true>);
+      else if (p.D == 192) go(paged_window_attention_mma_kernel<192, 128, true>);
+      else if (p.D == 64) go(paged_window_attention_mma_kernel<64, 64, true>);
+      else go(paged_window_attention_mma_kernel<128, 128, true>);
+    } else if (p.D == 64 && p.Dv == 64) go(paged_window_attention_mma_kernel<64, 64, false>);
+    else if (p.D == 64) go(paged_window_attention_mma_kernel<64, 128, false>);
+    else if (p.Dv == 64) go(paged_window_attention_mma_kernel<128, 64, false>);
+    else go(paged_window_attention_mma_kernel<128, 128, false>);
     return;
   }
   // few queries (decode steps): one block per query, its warps split the keys; otherwise one warp per query
@@ -1179,6 +1331,7 @@ void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStrea
   // split mode: one warp per 32 visible keys (bounded by the window or by the pages a row can hold), 4 to 32 warps
   long long span = (long long)p.max_blocks * p.page;
   if (p.window > 0) span = std::min<long long>(span, (long long)p.window + p.keep_first);
+  if (p.chunk > 0) span = std::min<long long>(span, (long long)p.chunk);
   const int nwarps = split ? (int)std::min<long long>(32, std::max<long long>(ATT_WARPS, (span + 31) / 32)) : ATT_WARPS;
   const size_t smem = sizeof(float) * (size_t)(nwarps * (p.D + p.Dv + 2));
   const unsigned grid = (unsigned)(split ? nq : (nq + ATT_WARPS - 1) / ATT_WARPS);

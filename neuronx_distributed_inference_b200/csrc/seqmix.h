@@ -28,29 +28,68 @@ struct StreamAddParams {
 };
 void stream_add_rmsnorm_launch(const StreamAddParams& p, bool y_lp, bool h_lp, cudaStream_t st);
 
+// p points at the latent slice of the projection rows.  rot > 0: the `rot` channels behind the latent are rotated (rotate-half
+// layout, cos / sin [B, T, rot / 2]) and stored behind the latent in the cache row of R + rot numbers.  q_rank > 0: channels
+// [0, q_rank) of the rows at `q_in` (same strides) are RMS-normalised with q_w into q_out [B, T, q_rank].
 void latent_norm_append_launch(const void* p, long long p_sb, long long p_st, const float* w, void* cache, const int* block_table,
                                const int* ctx_len, const int* q_len, int B, int T, int R, int page, int max_blocks, float eps, bool lp,
-                               void* rows_out, cudaStream_t st);      // rows_out: [B, T, R] copy of the live rows in token order, or null
+                               void* rows_out, int rot, const float* cos, const float* sin, const void* q_in, int q_rank, const float* q_w,
+                               void* q_out, cudaStream_t st);      // rows_out: [B, T, R + rot] copy of the live rows in token order, or null
+
+// dst[b, t, h, Dd - rot ...] = rotate_half(src[b, t, h, Ds - rot ...]) with cos / sin [B * T, rot / 2]
+void rope_half_tail_launch(const void* src, void* dst, const float* cos, const float* sin, long long tokens, int H, int Ds, int Dd, int rot, bool lp,
+                           cudaStream_t st);
+
+// s = x + [y1] + [y2]; h = rms_unit(s) * w; out = h + sum_j cw[:, j] * h_(t - K + 1 + j), the rows before a portion from the fp32 state
+// line (stream rows, normalised like the new ones; zero when ctx_len == 0).  cw null: out = h.
+struct StreamConvParams {
+  const float* x;            // [B, T, W]
+  const void *y1, *y2;       // [B, T, W] or null, each bf16 or fp32
+  int y1_lp, y2_lp;
+  const float *w, *cw;       // [W], [W, K] or null
+  const float* state;        // [lines, K - 1, W] or null (K == 1)
+  const int *lines, *ctx_len, *q_len;
+  float* s;                  // [B, T, W]
+  void* out;                 // [B, T, W] bf16 or fp32
+  int B, T, W, K;
+  float eps;
+};
+void stream_norm_conv_launch(const StreamConvParams& p, bool out_lp, cudaStream_t st);
+
+// y[tok, :] += x[tok, :] * sum_j topk_w[tok, j] [topk_i[tok, j] >= num_experts] (fp32 sum, in place)
+void identity_expert_add_launch(void* y, const void* x, const float* topk_w, const int* topk_i, int N, int H, int k, int num_experts, bool lp,
+                                cudaStream_t st);
 
 // x [rows, H, D] *= sigmoid(gate[row, h]) in place; gate rows are g_stride elements apart; D a multiple of 16 bytes
 void head_gate_mul_launch(void* x, const void* gate, long long g_stride, long long rows, int H, int D, bool lp, cudaStream_t st);
 
-// act codes: 1 relu, 2 relu^2, 3 silu, 4 tanh-gelu
-void gated_act_mul_launch(const void* gate, const void* other, long long o_stride, void* out, long long rows, int C, int act, bool lp,
-                          cudaStream_t st);
+// act codes: 1 relu, 2 relu^2, 3 silu, 4 tanh-gelu, 5 sigmoid.  on_other: out = gate * act(other) instead of act(gate) * other.
+// g_stride: elements between rows of `gate` (C when dense).
+void gated_act_mul_launch(const void* gate, long long g_stride, const void* other, long long o_stride, void* out, long long rows, int C, int act,
+                          bool on_other, bool lp, cudaStream_t st);
 void unary_act_launch(const void* x, void* out, long long n, int act, bool lp, cudaStream_t st);
 
 // Two-matrix experts y = W_down act(W_up x) on a device-side permutation (moe_plain.cu); T = bf16 or fp32, any sizes.
 void moe_plain_gather_launch(const void* x, const int* row_entry, const int* tile_expert, void* xp, int R, int H, int k, bool lp, cudaStream_t st);
 void moe_plain_gemm_launch(const void* a, const void* w, void* c, int R, int N, int K, int act, const int* tile_expert, bool lp, cudaStream_t st);
 void moe_plain_combine_launch(const void* y, const float* topk_w, const int* pos, void* out, int N, int H, int k, bool lp, cudaStream_t st);
+// gated: w_up holds [gate; up] rows ([E, 2 I, H]) and the hidden row is act(gate . x) * (up . x)
 void moe_plain_decode_launch(const void* x, const void* w_up, const void* w_down, const float* topk_w, const int* topk_i, void* h, void* out,
-                             int N, int k, int H, int I, int expert_offset, int e_local, int act, bool lp, cudaStream_t st);
+                             int N, int k, int H, int I, int expert_offset, int e_local, int act, bool gated, bool lp, cudaStream_t st);
+// h[r, i] = act(gu[r, i]) * gu[r, I + i] for the rows of used 128-row tiles
+void moe_plain_gate_mul_launch(const void* gu, void* h, int R, int I, int act, const int* tile_expert, bool lp, cudaStream_t st);
 
 // fp32 router: logits = x W^T (x bf16 or fp32, W fp32 [E, W]) on CUDA cores with the rows in shared memory, then per token the
-// sigmoid scores of the k largest, divided by their sum + renorm_eps when renorm_eps >= 0.  `logits` [N, E] is written and read.
-void router_sigmoid_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
-                                float renorm_eps, bool lp, cudaStream_t st);
+// scores (sigmoid, or softmax over all E) of the k experts with the largest score + correction among the `keep` best of `groups` equal
+// groups of neighbours, divided by their sum + renorm_eps when renorm_eps >= 0, times scale.  `logits` [N, E] is written and read.
+struct RouterSelect {
+  int softmax;               // 0: sigmoid scores
+  const float* correction;   // [E] or null: added to the scores for the choice only
+  int groups, keep;          // groups <= 1: no group limit
+  float renorm_eps, scale;
+};
+void router_topk_launch(const void* x, const float* w, float* logits, float* topk_w, int* topk_i, int N, int W, int E, int k,
+                        const RouterSelect& sel, bool lp, cudaStream_t st);
 
 void short_conv_launch(const void* u, long long u_sb, long long u_st, const float* w, const float* bias, const void* state,
                        const int* lines, const int* ctx_len, const int* q_len, float* y, int B, int T, int C, int K, bool silu, bool lp,
@@ -86,6 +125,10 @@ struct WindowAttnParams {
   float scale, softcap;
   const float* sinks;       // [Hq] or null: exp(sinks[h]) joins the softmax denominator of head h (no key, no value)
   int gate_per_head;        // 1: gate is [B, T, Hq], one sigmoid factor per head instead of one per output channel
+  int chunk;                // > 0: key j is visible from position p only when j / chunk == p / chunk (instead of a window)
+  const float* slopes;      // [Hq] or null: slopes[h] * (p - j) is taken off the score of head h
+  long long v_rs;           // elements between the value rows of neighbouring (token, kv head) pairs; Dv <= v_rs (values that are a
+                            // prefix of a wider cache row: v_cache = k_cache, v_rs = D)
 };
 void paged_window_attention_launch(const WindowAttnParams& p, bool lp, cudaStream_t st);
 

@@ -89,8 +89,8 @@ void short_conv_update(const at::Tensor& u, at::Tensor state, const at::Tensor& 
 }
 
 at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w, const at::Tensor& state, const at::Tensor& lines,
-                                   const at::Tensor& ctx, const at::Tensor& qlen, const at::Tensor& q_norm_w, const OptT& k_norm_w, double eps,
-                                   int64_t n_q, int64_t n_kv, int64_t D, int64_t Dv, const at::Tensor& cos, const at::Tensor& sin,
+                                   const at::Tensor& ctx, const at::Tensor& qlen, const OptT& q_norm_w, const OptT& k_norm_w, double eps,
+                                   int64_t n_q, int64_t n_kv, int64_t D, int64_t Dv, const OptT& cos, const OptT& sin,
                                    at::Tensor k_cache, at::Tensor v_cache, const OptT& block_table) {
   check_act(p, "conv_qknorm_rope_append projections");
   check_rows(p, "conv_qknorm_rope_append projections");
@@ -103,25 +103,33 @@ at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w
   check_i32(lines, B, "lines");
   check_i32(ctx, B, "ctx_len");
   check_i32(qlen, B, "q_len");
-  check_f32(q_norm_w, "q norm weight");
-  TORCH_CHECK(q_norm_w.numel() == n_q * D);
-  check_f32(cos, "cos");
-  check_f32(sin, "sin");
-  TORCH_CHECK(cos.dim() == 3 && cos.size(0) == B && cos.size(1) == T && sin.sizes() == cos.sizes());
-  const int64_t R = 2 * cos.size(2);
+  if (q_norm_w.has_value()) {
+    check_f32(*q_norm_w, "q norm weight");
+    TORCH_CHECK(q_norm_w->numel() == n_q * D);
+  }
+  int64_t R = 0;
+  if (cos.has_value()) {      // no tables: no rotation
+    TORCH_CHECK(sin.has_value());
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 3 && cos->size(0) == B && cos->size(1) == T && sin->sizes() == cos->sizes());
+    R = 2 * cos->size(2);
+  }
   TORCH_CHECK(R <= D, "rotated channels exceed the head size");
   ConvQkParams a{};
   if (n_kv > 0) {
-    TORCH_CHECK(k_norm_w.has_value() && block_table.has_value());
-    check_f32(*k_norm_w, "k norm weight");
-    TORCH_CHECK(k_norm_w->numel() == n_kv * D);
+    TORCH_CHECK(block_table.has_value());
+    if (k_norm_w.has_value()) {
+      check_f32(*k_norm_w, "k norm weight");
+      TORCH_CHECK(k_norm_w->numel() == n_kv * D);
+      a.k_norm_w = k_norm_w->data_ptr<float>();
+    }
     TORCH_CHECK(k_cache.is_cuda() && k_cache.scalar_type() == p.scalar_type() && k_cache.is_contiguous() && k_cache.dim() == 4 &&
                 k_cache.size(2) == n_kv && k_cache.size(3) == D, "k cache [blocks, page, kv heads, D] of the activation type");
     TORCH_CHECK(v_cache.is_cuda() && v_cache.scalar_type() == p.scalar_type() && v_cache.is_contiguous() && v_cache.dim() == 4 &&
                 v_cache.size(0) == k_cache.size(0) && v_cache.size(1) == k_cache.size(1) && v_cache.size(2) == n_kv && v_cache.size(3) == Dv);
     TORCH_CHECK(block_table->is_cuda() && block_table->scalar_type() == at::kInt && block_table->is_contiguous() && block_table->dim() == 2 &&
                 block_table->size(0) == B);
-    a.k_norm_w = k_norm_w->data_ptr<float>();
     a.k_cache = k_cache.data_ptr();
     a.v_cache = v_cache.data_ptr();
     a.block_table = block_table->data_ptr<int>();
@@ -133,8 +141,9 @@ at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w
   a.p = p.data_ptr(); a.p_sb = p.stride(0); a.p_st = p.stride(1);
   a.conv_w = conv_w.data_ptr<float>(); a.state = state.data_ptr();
   a.lines = lines.data_ptr<int>(); a.ctx_len = ctx.data_ptr<int>(); a.q_len = qlen.data_ptr<int>();
-  a.q_norm_w = q_norm_w.data_ptr<float>();
-  a.cos = cos.data_ptr<float>(); a.sin = sin.data_ptr<float>();
+  a.q_norm_w = q_norm_w.has_value() ? q_norm_w->data_ptr<float>() : nullptr;
+  a.cos = cos.has_value() ? cos->data_ptr<float>() : nullptr;
+  a.sin = sin.has_value() ? sin->data_ptr<float>() : nullptr;
   a.q_out = q.data_ptr();
   a.B = (int)B; a.T = (int)T; a.K = (int)K; a.n_q = (int)n_q; a.n_kv = (int)n_kv; a.D = (int)D; a.Dv = (int)Dv; a.R = (int)R;
   a.eps = (float)eps;
@@ -144,14 +153,17 @@ at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w
 
 at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table,
                                   const at::Tensor& ctx, const at::Tensor& qlen, double scale, double softcap, int64_t window,
-                                  int64_t keep_first, const OptT& gate, const OptT& sinks, bool gate_per_head) {
+                                  int64_t keep_first, const OptT& gate, const OptT& sinks, bool gate_per_head, int64_t chunk, const OptT& slopes,
+                                  int64_t value_dim) {
   check_act(q, "paged_window_attention q");
   TORCH_CHECK(q.dim() == 4 && q.is_contiguous());
   const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), D = q.size(3);
   TORCH_CHECK(k_cache.is_cuda() && k_cache.scalar_type() == q.scalar_type() && k_cache.is_contiguous() && k_cache.dim() == 4 && k_cache.size(3) == D);
   TORCH_CHECK(v_cache.is_cuda() && v_cache.scalar_type() == q.scalar_type() && v_cache.is_contiguous() && v_cache.dim() == 4 &&
               v_cache.size(0) == k_cache.size(0) && v_cache.size(1) == k_cache.size(1) && v_cache.size(2) == k_cache.size(2));
-  const int64_t G = k_cache.size(2), Dv = v_cache.size(3);
+  // value_dim: the value of a key is the first value_dim channels of its row in v_cache
+  const int64_t G = k_cache.size(2), Dv = value_dim;
+  TORCH_CHECK(Dv >= 1 && Dv <= v_cache.size(3) && chunk >= 0 && !(chunk > 0 && window > 0), "paged_window_attention: value size / mask");
   TORCH_CHECK(Hq % G == 0 && Dv <= SEQMIX_MAX_VDIM, "paged_window_attention: heads must divide, value size <= ", SEQMIX_MAX_VDIM);
   TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == at::kInt && block_table.is_contiguous() && block_table.dim() == 2 &&
               block_table.size(0) == B);
@@ -170,6 +182,13 @@ at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache
     TORCH_CHECK(sinks->numel() == Hq, "sinks: one per query head");
     a.sinks = sinks->data_ptr<float>();
   }
+  if (slopes.has_value()) {
+    check_f32(*slopes, "slopes");
+    TORCH_CHECK(slopes->numel() == Hq, "slopes: one per query head");
+    a.slopes = slopes->data_ptr<float>();
+  }
+  a.chunk = (int)chunk;
+  a.v_rs = v_cache.size(3);
   c10::cuda::CUDAGuard guard(q.device());
   auto out = at::zeros({B, T, Hq * Dv}, q.options());
   a.q = q.data_ptr(); a.k_cache = k_cache.data_ptr(); a.v_cache = v_cache.data_ptr();
@@ -277,28 +296,43 @@ std::tuple<at::Tensor, OptT, OptT> stream_add_rmsnorm(const OptT& x, const OptT&
   return {s, s_lp, h};
 }
 
-OptT latent_norm_append(const at::Tensor& p, int64_t offset, int64_t rank, const at::Tensor& w, double eps, at::Tensor cache,
-                        const at::Tensor& block_table, const at::Tensor& ctx, const at::Tensor& qlen, bool emit_rows) {
+std::tuple<OptT, OptT> latent_norm_append(const at::Tensor& p, int64_t offset, int64_t rank, const at::Tensor& w, double eps, at::Tensor cache,
+                                          const at::Tensor& block_table, const at::Tensor& ctx, const at::Tensor& qlen, bool emit_rows, int64_t rot,
+                                          const OptT& cos, const OptT& sin, int64_t q_rank, const OptT& q_w) {
   check_act(p, "latent_norm_append input");
   check_rows(p, "latent_norm_append input");
   const int64_t B = p.size(0), T = p.size(1);
-  TORCH_CHECK(offset >= 0 && rank >= 1 && offset + rank <= p.size(2), "latent_norm_append: slice outside the row");
+  TORCH_CHECK(offset >= 0 && rank >= 1 && rot >= 0 && rot % 2 == 0 && offset + rank + rot <= p.size(2), "latent_norm_append: slice outside the row");
+  if (rot > 0) {
+    TORCH_CHECK(cos.has_value() && sin.has_value());
+    check_f32(*cos, "cos");
+    check_f32(*sin, "sin");
+    TORCH_CHECK(cos->numel() == B * T * (rot / 2) && sin->numel() == cos->numel(), "cos / sin [B, T, rot / 2]");
+  }
+  if (q_rank > 0) {
+    TORCH_CHECK(q_w.has_value() && q_rank <= p.size(2));
+    check_f32(*q_w, "query latent norm weight");
+    TORCH_CHECK(q_w->numel() == q_rank);
+  }
   check_f32(w, "latent norm weight");
   TORCH_CHECK(w.numel() == rank);
   TORCH_CHECK(cache.is_cuda() && cache.scalar_type() == p.scalar_type() && cache.is_contiguous() && cache.dim() == 4 && cache.size(2) == 1 &&
-              cache.size(3) == rank, "latent cache [blocks, page, 1, rank] of the activation type");
+              cache.size(3) == rank + rot, "latent cache [blocks, page, 1, rank + rotated part] of the activation type");
   TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == at::kInt && block_table.is_contiguous() && block_table.dim() == 2 &&
               block_table.size(0) == B);
   check_i32(ctx, B, "ctx_len");
   check_i32(qlen, B, "q_len");
   c10::cuda::CUDAGuard guard(p.device());
   const char* base = (const char*)p.data_ptr() + offset * p.element_size();
-  OptT rows;
-  if (emit_rows) rows = at::zeros({B, T, 1, rank}, p.options());      // rows past q_len stay zero
+  OptT rows, cq;
+  if (emit_rows) rows = at::zeros({B, T, 1, rank + rot}, p.options());      // rows past q_len stay zero
+  if (q_rank > 0) cq = at::zeros({B, T, q_rank}, p.options());
   latent_norm_append_launch(base, p.stride(0), p.stride(1), w.data_ptr<float>(), cache.data_ptr(), block_table.data_ptr<int>(), ctx.data_ptr<int>(),
                             qlen.data_ptr<int>(), (int)B, (int)T, (int)rank, (int)cache.size(1), (int)block_table.size(1), (float)eps, is_lp(p),
-                            rows.has_value() ? rows->data_ptr() : nullptr, stream());
-  return rows;
+                            rows.has_value() ? rows->data_ptr() : nullptr, (int)rot, rot > 0 ? cos->data_ptr<float>() : nullptr,
+                            rot > 0 ? sin->data_ptr<float>() : nullptr, p.data_ptr(), (int)q_rank, q_rank > 0 ? q_w->data_ptr<float>() : nullptr,
+                            cq.has_value() ? cq->data_ptr() : nullptr, stream());
+  return {rows, cq};
 }
 
 void head_gate_mul(at::Tensor x, const at::Tensor& gate) {
@@ -313,14 +347,14 @@ void head_gate_mul(at::Tensor x, const at::Tensor& gate) {
   head_gate_mul_launch(x.data_ptr(), gate.data_ptr(), gate.stride(1), x.size(0) * x.size(1), (int)x.size(2), (int)x.size(3), is_lp(x), stream());
 }
 
-at::Tensor gated_act_mul(const at::Tensor& gate, const at::Tensor& other, int64_t act) {
+at::Tensor gated_act_mul(const at::Tensor& gate, const at::Tensor& other, int64_t act, bool on_other) {
   check_act(gate, "gated_act_mul gate");
   TORCH_CHECK(gate.dim() == 2 && gate.is_contiguous() && other.is_cuda() && other.scalar_type() == gate.scalar_type() && other.dim() == 2 &&
               other.sizes() == gate.sizes() && other.stride(1) == 1, "gated_act_mul: [rows, C] inputs of one type, the second with a row stride");
   c10::cuda::CUDAGuard guard(gate.device());
   auto out = at::empty_like(gate);
-  gated_act_mul_launch(gate.data_ptr(), other.data_ptr(), other.stride(0), out.data_ptr(), gate.size(0), (int)gate.size(1), (int)act, is_lp(gate),
-                       stream());
+  gated_act_mul_launch(gate.data_ptr(), gate.stride(0), other.data_ptr(), other.stride(0), out.data_ptr(), gate.size(0), (int)gate.size(1), (int)act,
+                       on_other, is_lp(gate), stream());
   return out;
 }
 
@@ -336,12 +370,14 @@ at::Tensor unary_act(const at::Tensor& x, int64_t act) {
 // Routed two-matrix experts: x [N, H], w_up [E, I, H], w_down [E, H, I] (activation type), topk_w fp32 / topk_i int32 [N, k].
 // `tc`: bf16 with H and I in multiples of 64 -> grouped tcgen05 GEMMs, the activation as an elementwise pass between them.
 at::Tensor moe_plain(const at::Tensor& x, const at::Tensor& w_up, const at::Tensor& w_down, const at::Tensor& topk_w, const at::Tensor& topk_i,
-                     int64_t expert_offset, int64_t act, bool tc) {
+                     int64_t expert_offset, int64_t act, bool tc, bool gated) {
   check_act(x, "moe_plain x");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && w_up.dim() == 3 && w_down.dim() == 3 && w_up.is_contiguous() && w_down.is_contiguous() &&
               w_up.scalar_type() == x.scalar_type() && w_down.scalar_type() == x.scalar_type() && w_up.is_cuda() && w_down.is_cuda());
-  const int N = (int)x.size(0), H = (int)x.size(1), E = (int)w_up.size(0), I = (int)w_up.size(1), k = (int)topk_i.size(1);
-  TORCH_CHECK(w_up.size(2) == H && w_down.size(0) == E && w_down.size(1) == H && w_down.size(2) == I, "moe_plain: w_up [E, I, H], w_down [E, H, I]");
+  // gated: w_up holds [gate; up] rows, [E, 2 I, H], and the hidden row is act(gate) * up
+  const int N = (int)x.size(0), H = (int)x.size(1), E = (int)w_up.size(0), I = (int)w_down.size(2), k = (int)topk_i.size(1);
+  TORCH_CHECK(w_up.size(1) == (gated ? 2 : 1) * I && w_up.size(2) == H && w_down.size(0) == E && w_down.size(1) == H && !(gated && tc),
+              "moe_plain: w_up [E, I, H] ([E, 2 I, H] gated), w_down [E, H, I]");
   TORCH_CHECK(topk_w.is_cuda() && topk_w.scalar_type() == at::kFloat && topk_i.is_cuda() && topk_i.scalar_type() == at::kInt && topk_w.is_contiguous() &&
               topk_i.is_contiguous() && topk_w.numel() == (int64_t)N * k && topk_i.size(0) == N && k <= 64 && E <= 512);
   const bool lp = is_lp(x);
@@ -352,7 +388,7 @@ at::Tensor moe_plain(const at::Tensor& x, const at::Tensor& w_up, const at::Tens
   if (N * k <= 32) {        // decode steps: weight-streaming kernels, no permutation
     auto h = at::empty({(int64_t)N * k, I}, x.options());
     moe_plain_decode_launch(x.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), topk_w.data_ptr<float>(), topk_i.data_ptr<int>(), h.data_ptr(),
-                            out.data_ptr(), N, k, H, I, (int)expert_offset, E, (int)act, lp, st);
+                            out.data_ptr(), N, k, H, I, (int)expert_offset, E, (int)act, gated, lp, st);
     return out;
   }
   const int64_t R = (((int64_t)N * k + (int64_t)E * 127) + 127) / 128 * 128;   // static bound: graph-stable shapes
@@ -374,13 +410,20 @@ at::Tensor moe_plain(const at::Tensor& x, const at::Tensor& w_up, const at::Tens
     return out;
   }
   moe_plain_gather_launch(x.data_ptr(), row_entry.data_ptr<int>(), tile_expert.data_ptr<int>(), xp.data_ptr(), (int)R, H, k, lp, st);
-  moe_plain_gemm_launch(xp.data_ptr(), w_up.data_ptr(), h.data_ptr(), (int)R, I, H, (int)act, tile_expert.data_ptr<int>(), lp, st);
+  if (gated) {
+    auto gu = at::empty({R, 2 * (int64_t)I}, x.options());
+    moe_plain_gemm_launch(xp.data_ptr(), w_up.data_ptr(), gu.data_ptr(), (int)R, 2 * I, H, 0, tile_expert.data_ptr<int>(), lp, st);
+    moe_plain_gate_mul_launch(gu.data_ptr(), h.data_ptr(), (int)R, I, (int)act, tile_expert.data_ptr<int>(), lp, st);
+  } else {
+    moe_plain_gemm_launch(xp.data_ptr(), w_up.data_ptr(), h.data_ptr(), (int)R, I, H, (int)act, tile_expert.data_ptr<int>(), lp, st);
+  }
   moe_plain_gemm_launch(h.data_ptr(), w_down.data_ptr(), y.data_ptr(), (int)R, H, I, 0, tile_expert.data_ptr<int>(), lp, st);
   moe_plain_combine_launch(y.data_ptr(), topk_w.data_ptr<float>(), pos.data_ptr<int>(), out.data_ptr(), N, H, k, lp, st);
   return out;
 }
 
-std::tuple<at::Tensor, at::Tensor, at::Tensor> router_sigmoid_topk(const at::Tensor& x, const at::Tensor& w, int64_t k, double renorm_eps) {
+std::tuple<at::Tensor, at::Tensor, at::Tensor> router_topk(const at::Tensor& x, const at::Tensor& w, int64_t k, double renorm_eps, bool softmax,
+                                                           const OptT& correction, int64_t groups, int64_t keep, double scale) {
   check_act(x, "router input");
   check_f32(w, "router weight");
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && w.dim() == 2 && w.size(1) == x.size(1) && k >= 1 && k <= w.size(0));
@@ -390,15 +433,95 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> router_sigmoid_topk(const at::Ten
   auto logits = at::empty({N, E}, f32);
   auto tw = at::empty({N, k}, f32);
   auto ti = at::empty({N, k}, x.options().dtype(at::kInt));
-  router_sigmoid_topk_launch(x.data_ptr(), w.data_ptr<float>(), logits.data_ptr<float>(), tw.data_ptr<float>(), ti.data_ptr<int>(), N, W, E, (int)k,
-                             (float)renorm_eps, is_lp(x), stream());
+  RouterSelect sel{};
+  sel.softmax = softmax ? 1 : 0;
+  if (correction.has_value()) {
+    check_f32(*correction, "router score correction");
+    TORCH_CHECK(correction->numel() == E);
+    sel.correction = correction->data_ptr<float>();
+  }
+  sel.groups = (int)groups; sel.keep = (int)keep; sel.renorm_eps = (float)renorm_eps; sel.scale = (float)scale;
+  router_topk_launch(x.data_ptr(), w.data_ptr<float>(), logits.data_ptr<float>(), tw.data_ptr<float>(), ti.data_ptr<int>(), N, W, E, (int)k, sel,
+                     is_lp(x), stream());
   return {logits, tw, ti};
+}
+
+void rope_half_tail(const at::Tensor& src, at::Tensor dst, int64_t rot, const at::Tensor& cos, const at::Tensor& sin) {
+  check_act(src, "rope_half_tail source");
+  TORCH_CHECK(src.dim() == 4 && dst.dim() == 4 && src.is_contiguous() && dst.is_contiguous() && dst.is_cuda() && dst.scalar_type() == src.scalar_type() &&
+              src.size(0) == dst.size(0) && src.size(1) == dst.size(1) && src.size(2) == dst.size(2) && rot % 2 == 0 && rot <= src.size(3) &&
+              rot <= dst.size(3), "rope_half_tail: [B, T, H, D] tensors of one type");
+  check_f32(cos, "cos");
+  check_f32(sin, "sin");
+  const int64_t tokens = src.size(0) * src.size(1);
+  TORCH_CHECK(cos.numel() == tokens * (rot / 2) && sin.numel() == cos.numel(), "cos / sin [B, T, rot / 2]");
+  c10::cuda::CUDAGuard guard(src.device());
+  rope_half_tail_launch(src.data_ptr(), dst.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), tokens, (int)src.size(2), (int)src.size(3),
+                        (int)dst.size(3), (int)rot, is_lp(src), stream());
+}
+
+std::tuple<at::Tensor, at::Tensor> stream_norm_conv(const at::Tensor& x, const OptT& y1, const OptT& y2, const at::Tensor& w, const OptT& cw,
+                                                    const OptT& state, const OptT& lines, const at::Tensor& ctx, const at::Tensor& qlen, double eps,
+                                                    bool out_lp) {
+  check_f32(x, "stream_norm_conv x");
+  TORCH_CHECK(x.dim() == 3, "stream_norm_conv: x [B, T, W]");
+  const int64_t B = x.size(0), T = x.size(1), W = x.size(2);
+  StreamConvParams a{};
+  for (const OptT* y : {&y1, &y2}) {
+    if (!y->has_value()) continue;
+    check_act(**y, "stream_norm_conv addend");
+    TORCH_CHECK((*y)->is_contiguous() && (*y)->sizes() == x.sizes());
+  }
+  if (y1.has_value()) { a.y1 = y1->data_ptr(); a.y1_lp = is_lp(*y1); }
+  if (y2.has_value()) { a.y2 = y2->data_ptr(); a.y2_lp = is_lp(*y2); }
+  check_f32(w, "stream_norm_conv norm weight");
+  TORCH_CHECK(w.numel() == W);
+  a.K = 1;
+  if (cw.has_value()) {
+    check_f32(*cw, "stream_norm_conv taps");
+    TORCH_CHECK(cw->dim() == 2 && cw->size(0) == W && cw->size(1) >= 1 && cw->size(1) <= SEQMIX_MAX_TAPS, "taps [W, K], K <= ", SEQMIX_MAX_TAPS);
+    a.K = (int)cw->size(1);
+    a.cw = cw->data_ptr<float>();
+    if (a.K > 1) {
+      TORCH_CHECK(state.has_value() && lines.has_value());
+      check_f32(*state, "stream_norm_conv state");
+      TORCH_CHECK(state->dim() == 3 && state->size(1) == a.K - 1 && state->size(2) == W, "state [lines, K - 1, W] float32");
+      check_i32(*lines, B, "lines");
+      a.state = state->data_ptr<float>();
+      a.lines = lines->data_ptr<int>();
+    }
+  }
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto s = at::zeros_like(x);                                                        // rows past q_len stay zero
+  auto out = at::zeros(x.sizes(), x.options().dtype(out_lp ? at::kBFloat16 : at::kFloat));
+  a.x = x.data_ptr<float>(); a.w = w.data_ptr<float>();
+  a.ctx_len = ctx.data_ptr<int>(); a.q_len = qlen.data_ptr<int>();
+  a.s = s.data_ptr<float>(); a.out = out.data_ptr();
+  a.B = (int)B; a.T = (int)T; a.W = (int)W; a.eps = (float)eps;
+  stream_norm_conv_launch(a, out_lp, stream());
+  return {s, out};
+}
+
+void identity_expert_add(at::Tensor y, const at::Tensor& x, const at::Tensor& topk_w, const at::Tensor& topk_i, int64_t num_experts) {
+  check_act(y, "identity_expert_add y");
+  TORCH_CHECK(y.dim() == 2 && y.is_contiguous() && x.is_cuda() && x.is_contiguous() && x.scalar_type() == y.scalar_type() && x.sizes() == y.sizes());
+  const int64_t N = y.size(0), k = topk_i.size(1);
+  TORCH_CHECK(topk_w.is_cuda() && topk_w.scalar_type() == at::kFloat && topk_w.is_contiguous() && topk_w.numel() == N * k && topk_i.is_cuda() &&
+              topk_i.scalar_type() == at::kInt && topk_i.is_contiguous() && topk_i.size(0) == N);
+  c10::cuda::CUDAGuard guard(y.device());
+  identity_expert_add_launch(y.data_ptr(), x.data_ptr(), topk_w.data_ptr<float>(), topk_i.data_ptr<int>(), (int)N, (int)y.size(1), (int)k,
+                             (int)num_experts, is_lp(y), stream());
 }
 
 }  // namespace
 
 void register_seqmix(pybind11::module_& m) {
-  m.def("router_sigmoid_topk", &router_sigmoid_topk);
+  m.def("router_topk", &router_topk);
+  m.def("rope_half_tail", &rope_half_tail);
+  m.def("stream_norm_conv", &stream_norm_conv);
+  m.def("identity_expert_add", &identity_expert_add);
   m.def("stream_add_rmsnorm", &stream_add_rmsnorm);
   m.def("latent_norm_append", &latent_norm_append);
   m.def("head_gate_mul", &head_gate_mul);
