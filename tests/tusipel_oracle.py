@@ -22,7 +22,8 @@ def causal_conv(u, w):
 
 
 def canon(h, w):
-    return h + causal_conv(h, w)
+    """What a sublayer reads; a stack without these convolutions (no taps in its configuration) reads h itself."""
+    return h if w is None else h + causal_conv(h, w)
 
 
 def yarn_tables(T, rot):
@@ -158,14 +159,14 @@ def forward(cfg, w, tokens, streams=None):
         if again:
             x = x + x0
         spec, p = cfg["layers"][i], f"l{i}."
-        h = canon(block_norm(x, w[p + "norm1"], eps), w[p + "canon1"])
+        h = canon(block_norm(x, w[p + "norm1"], eps), w.get(p + "canon1"))
         if spec["type"] == "latent_attention":
             x = x + latent_attention(h, w, p + "mix.", spec["mixer"], eps)
         else:
             x = x + conv_attention(h, w, p + "mix.", spec["mixer"])
         f = spec.get("mlp")
         if f is not None:
-            h = canon(block_norm(x, w[p + "norm2"], eps), w[p + "canon2"])
+            h = canon(block_norm(x, w[p + "norm2"], eps), w.get(p + "canon2"))
             x = x + (dense_ff(h, w, p + "mlp.", f) if f["kind"] == "dense" else moe_ff(h, w, p + "mlp.", f))
         if streams is not None:
             streams.append(x.clone())
