@@ -989,11 +989,21 @@ __device__ __forceinline__ float ld_any(const void* p, long long i, int lp) {
   return lp ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i];
 }
 
+// rows past q_len are written as zeros by every variant (the outputs are allocated uninitialised)
+template <typename TO>
+__device__ __forceinline__ void zero_stream_row(const StreamConvParams& p, int b, int t) {
+  const long long o = ((long long)b * p.T + t) * p.W;
+  for (int c = threadIdx.x; c < p.W; c += blockDim.x) {
+    p.s[o + c] = 0.f;
+    stf((TO*)p.out + o + c, 0.f);
+  }
+}
+
 template <typename TO>
 __global__ void __launch_bounds__(256) stream_norm_conv_kernel(StreamConvParams p) {
   __shared__ float red[32];
   const int b = blockIdx.y, t = blockIdx.x;
-  if (t >= p.q_len[b]) return;
+  if (t >= p.q_len[b]) { zero_stream_row<TO>(p, b, t); return; }
   const int W = p.W, K = p.K;
   const bool has_ctx = p.ctx_len[b] > 0;
   const long long base = (long long)b * p.T * W;
@@ -1034,6 +1044,207 @@ __global__ void __launch_bounds__(256) stream_norm_conv_kernel(StreamConvParams 
         if (j == K - 1) { own = h; p.s[o0 + c] = v; }
       }
     stf((TO*)p.out + o0 + c, own + acc);
+  }
+}
+
+// The same with four channels per access and the K window rows held in registers (one pass over the inputs): W a multiple of 4,
+// K <= 4, W <= 4 * NCH * blockDim.x.
+__device__ __forceinline__ float4 ld4_any(const void* p, long long i, int lp) {
+  if (lp) {
+    const uint2 r = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)p + i);
+    return make_float4(bf16lo(r.x), bf16hi(r.x), bf16lo(r.y), bf16hi(r.y));
+  }
+  return *reinterpret_cast<const float4*>((const float*)p + i);
+}
+
+// addend modes: 0 absent, 1 fp32, 2 bf16.  The mode is a template parameter of the row loader so that the loads of all rows are
+// independent straight-line code (a branch per load would serialise them).
+template <int M>
+__device__ __forceinline__ void add4(float4& a, const void* y, long long o, float m) {
+  if constexpr (M == 1) {
+    const float4 v = *reinterpret_cast<const float4*>((const float*)y + o);
+    a.x += m * v.x; a.y += m * v.y; a.z += m * v.z; a.w += m * v.w;
+  } else if constexpr (M == 2) {
+    const uint2 r = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)y + o);
+    a.x += m * bf16lo(r.x); a.y += m * bf16hi(r.x); a.z += m * bf16lo(r.y); a.w += m * bf16hi(r.y);
+  }
+}
+
+// window rows first .. first + NR - 1 (token indices; negative: carried rows) of batch row b into registers, with their sums of squares.
+// Every load is issued unconditionally from a clamped, valid address and masked afterwards: no branch separates a load from the next,
+// so all of a thread's loads are in flight together.
+template <int M1, int M2, int K, int NCH, int NR>
+__device__ __forceinline__ void load_stream_rows(const StreamConvParams& p, long long base, const float* sl, bool has_ctx, int first, int limit,
+                                                 float4 (&v)[NR][NCH], float (&ss)[NR]) {
+  const int W = p.W;
+  const bool carried = has_ctx && sl != nullptr;
+#pragma unroll
+  for (int rr = 0; rr < NR; ++rr) {
+    const int i = first + rr;
+    const bool isnew = i >= 0;
+    const int ic = min(max(i, 0), p.T - 1), is = max(K - 1 + i, 0);
+    ss[rr] = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * blockDim.x + threadIdx.x) * 4, cc = min(c, W - 4);
+      const long long o = base + (long long)ic * W + cc;
+      const float* src = (isnew || !carried) ? p.x + o : sl + (long long)is * W + cc;
+      float4 a = *reinterpret_cast<const float4*>(src);
+      const float m = isnew ? 1.f : 0.f;
+      add4<M1>(a, p.y1, o, m);
+      add4<M2>(a, p.y2, o, m);
+      const bool ok = c < W && (isnew ? i < limit : carried);
+      if (!ok) a = make_float4(0.f, 0.f, 0.f, 0.f);
+      v[rr][ch] = a;
+      ss[rr] += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+    }
+  }
+}
+
+template <int K, int NCH, int NR>
+__device__ __forceinline__ void load_stream_rows_any(const StreamConvParams& p, long long base, const float* sl, bool has_ctx, int first, int limit,
+                                                     float4 (&v)[NR][NCH], float (&ss)[NR]) {
+  const int m1 = p.y1 ? (p.y1_lp ? 2 : 1) : 0, m2 = p.y2 ? (p.y2_lp ? 2 : 1) : 0;
+  switch (m1 * 3 + m2) {
+    case 0: load_stream_rows<0, 0, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 1: load_stream_rows<0, 1, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 2: load_stream_rows<0, 2, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 3: load_stream_rows<1, 0, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 4: load_stream_rows<1, 1, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 5: load_stream_rows<1, 2, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 6: load_stream_rows<2, 0, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    case 7: load_stream_rows<2, 1, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+    default: load_stream_rows<2, 2, K, NCH, NR>(p, base, sl, has_ctx, first, limit, v, ss); break;
+  }
+}
+
+template <typename TO, int K, int NCH>
+__global__ void __launch_bounds__(512) stream_norm_conv_vec_kernel(StreamConvParams p) {
+  __shared__ float red[K][32];
+  const int b = blockIdx.y, t = blockIdx.x;
+  if (t >= p.q_len[b]) { zero_stream_row<TO>(p, b, t); return; }
+  const int W = p.W, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const bool has_ctx = p.ctx_len[b] > 0;
+  const long long base = (long long)b * p.T * W;
+  const float* sl = p.state ? p.state + (long long)p.lines[b] * (K - 1) * W : nullptr;
+  float4 v[K][NCH];
+  float ss[K];
+  load_stream_rows_any<K, NCH, K>(p, base, sl, has_ctx, t - K + 1, t + 1, v, ss);
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    const float w = warp_sum(ss[j]);
+    if (lane == 0) red[j][warp] = w;
+  }
+  __syncthreads();
+  float r[K];
+#pragma unroll
+  for (int j = 0; j < K; ++j) r[j] = 1.f / sqrtf(warp_sum(lane < nw ? red[j][lane] : 0.f) / (float)W + p.eps);
+  const long long o0 = base + (long long)t * W;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * blockDim.x + threadIdx.x) * 4;
+    if (c >= W) continue;
+    const float4 wc = *reinterpret_cast<const float4*>(p.w + c);
+    const float wv[4] = {wc.x, wc.y, wc.z, wc.w};
+    float out[4];
+    float taps[4 * K];                                 // the taps of these four channels: cw[c .. c + 3][0 .. K - 1], contiguous
+    if (p.cw) {
+#pragma unroll
+      for (int q = 0; q < K; ++q) {
+        const float4 tq = *reinterpret_cast<const float4*>(p.cw + (long long)c * K + 4 * q);
+        taps[4 * q] = tq.x; taps[4 * q + 1] = tq.y; taps[4 * q + 2] = tq.z; taps[4 * q + 3] = tq.w;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float acc = 0.f, own = 0.f;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const float4 a = v[j][ch];
+        const float val = e == 0 ? a.x : (e == 1 ? a.y : (e == 2 ? a.z : a.w));
+        const float h = val * r[j] * wv[e];
+        if (p.cw) acc += taps[e * K + j] * h;
+        if (j == K - 1) own = h;
+      }
+      out[e] = own + acc;
+    }
+    *reinterpret_cast<float4*>(p.s + o0 + c) = v[K - 1][ch];
+    if constexpr (std::is_same<TO, float>::value) {
+      *reinterpret_cast<float4*>((float*)p.out + o0 + c) = make_float4(out[0], out[1], out[2], out[3]);
+    } else {
+      *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + o0 + c) = make_uint2(pack_bf16(out[0], out[1]), pack_bf16(out[2], out[3]));
+    }
+  }
+}
+
+// Block = TT consecutive tokens of one batch row: the TT + K - 1 stream rows they read are loaded once and normalised once (a token's
+// row serves the K - 1 tokens after it too), all in registers.  W <= 8 * blockDim.x.
+template <typename TO, int K, int NCH, int TT>
+__global__ void __launch_bounds__(256, NCH <= 2 ? 3 : 2) stream_norm_conv_tile_kernel(StreamConvParams p) {
+  constexpr int NR = TT + K - 1;
+  __shared__ float red[NR][32];
+  __shared__ float inv[NR];
+  const int b = blockIdx.y, t0 = blockIdx.x * TT, qn = p.q_len[b];
+  for (int i = 0; i < TT; ++i)
+    if (t0 + i >= qn && t0 + i < p.T) zero_stream_row<TO>(p, b, t0 + i);
+  if (t0 >= qn) return;
+  const int W = p.W, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const bool has_ctx = p.ctx_len[b] > 0;
+  const long long base = (long long)b * p.T * W;
+  const float* sl = p.state ? p.state + (long long)p.lines[b] * (K - 1) * W : nullptr;
+  float4 v[NR][NCH];
+  float ss[NR];
+  load_stream_rows_any<K, NCH, NR>(p, base, sl, has_ctx, t0 - (K - 1), qn, v, ss);
+#pragma unroll
+  for (int rr = 0; rr < NR; ++rr) {
+    const float w = warp_sum(ss[rr]);
+    if (lane == 0) red[rr][warp] = w;
+  }
+  __syncthreads();
+  for (int rr = warp; rr < NR; rr += nw) {             // one warp finishes a row: one accurate root and division per row, not per thread
+    const float tot = warp_sum(lane < nw ? red[rr][lane] : 0.f);
+    if (lane == 0) inv[rr] = 1.f / sqrtf(tot / (float)W + p.eps);
+  }
+  __syncthreads();
+  float r[NR];
+#pragma unroll
+  for (int rr = 0; rr < NR; ++rr) r[rr] = inv[rr];
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * blockDim.x + threadIdx.x) * 4;
+    if (c >= W) continue;
+    const float4 wc = *reinterpret_cast<const float4*>(p.w + c);
+    float taps[4 * K];                                 // the taps of these four channels: cw[c .. c + 3][0 .. K - 1], contiguous
+#pragma unroll
+    for (int q = 0; q < K; ++q) {
+      const float4 tq = p.cw ? *reinterpret_cast<const float4*>(p.cw + (long long)c * K + 4 * q) : make_float4(0.f, 0.f, 0.f, 0.f);
+      taps[4 * q] = tq.x; taps[4 * q + 1] = tq.y; taps[4 * q + 2] = tq.z; taps[4 * q + 3] = tq.w;
+    }
+#pragma unroll
+    for (int i = 0; i < TT; ++i)
+      if (t0 + i < qn) *reinterpret_cast<float4*>(p.s + base + (long long)(t0 + i) * W + c) = v[K - 1 + i][ch];
+#pragma unroll
+    for (int rr = 0; rr < NR; ++rr) {                  // the normalised rows, in place
+      float4 a = v[rr][ch];
+      a.x *= r[rr] * wc.x; a.y *= r[rr] * wc.y; a.z *= r[rr] * wc.z; a.w *= r[rr] * wc.w;
+      v[rr][ch] = a;
+    }
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+      if (t0 + i >= qn) continue;
+      float4 o = v[K - 1 + i][ch];
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const float4 h = v[i + j][ch];
+        o.x += taps[j] * h.x; o.y += taps[K + j] * h.y; o.z += taps[2 * K + j] * h.z; o.w += taps[3 * K + j] * h.w;
+      }
+      const long long oo = base + (long long)(t0 + i) * W + c;
+      if constexpr (std::is_same<TO, float>::value) {
+        *reinterpret_cast<float4*>((float*)p.out + oo) = o;
+      } else {
+        *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + oo) = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+      }
+    }
   }
 }
 
@@ -1200,6 +1411,37 @@ void rope_half_tail_launch(const void* src, void* dst, const float* cos, const f
 void stream_norm_conv_launch(const StreamConvParams& p, bool out_lp, cudaStream_t st) {
   if (p.B <= 0 || p.T <= 0) return;
   dim3 grid(p.T, p.B);
+  auto al = [](const void* q, size_t a) { return ((uintptr_t)q & (a - 1)) == 0; };
+  const int vt = p.W <= 512 ? 128 : (p.W <= 4096 ? 256 : 512);
+  const int need = (p.W + 4 * vt - 1) / (4 * vt), nch = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+  if (p.W % 4 == 0 && p.K <= 4 && need <= 4 && al(p.x, 16) && al(p.y1, p.y1_lp ? 8 : 16) && al(p.y2, p.y2_lp ? 8 : 16) && al(p.w, 16) && al(p.cw, 16) &&
+      al(p.state, 16) && al(p.s, 16) && al(p.out, out_lp ? 8 : 16)) {
+    if (p.W <= 4096 && p.T >= 2) {
+      // portions: two tokens per block share the rows they read (K + 1 rows instead of 2 K); 4 to 16 channels per thread
+      const int tt = p.W <= 1024 ? 128 : 256;
+      const int nc = p.W <= 4 * tt ? 1 : (p.W <= 8 * tt ? 2 : 4);
+      dim3 tg((p.T + 1) / 2, p.B);
+#define NXDI_SNT(TO, KK) if (nc == 4) stream_norm_conv_tile_kernel<TO, KK, 4, 2><<<tg, tt, 0, st>>>(p); \
+                         else if (nc == 2) stream_norm_conv_tile_kernel<TO, KK, 2, 2><<<tg, tt, 0, st>>>(p); \
+                         else stream_norm_conv_tile_kernel<TO, KK, 1, 2><<<tg, tt, 0, st>>>(p)
+#define NXDI_SNT_K(TO) switch (p.K) { case 1: NXDI_SNT(TO, 1); break; case 2: NXDI_SNT(TO, 2); break; case 3: NXDI_SNT(TO, 3); break; default: NXDI_SNT(TO, 4); }
+      if (out_lp) { NXDI_SNT_K(__nv_bfloat16) } else { NXDI_SNT_K(float) }
+#undef NXDI_SNT_K
+#undef NXDI_SNT
+      return;
+    }
+    auto go = [&](auto k1, auto k2, auto k4) {
+      if (nch == 1) k1<<<grid, vt, 0, st>>>(p);
+      else if (nch == 2) k2<<<grid, vt, 0, st>>>(p);
+      else k4<<<grid, vt, 0, st>>>(p);
+    };
+#define NXDI_SNC(TO, KK) go(stream_norm_conv_vec_kernel<TO, KK, 1>, stream_norm_conv_vec_kernel<TO, KK, 2>, stream_norm_conv_vec_kernel<TO, KK, 4>)
+#define NXDI_SNC_K(TO) switch (p.K) { case 1: NXDI_SNC(TO, 1); break; case 2: NXDI_SNC(TO, 2); break; case 3: NXDI_SNC(TO, 3); break; default: NXDI_SNC(TO, 4); }
+    if (out_lp) { NXDI_SNC_K(__nv_bfloat16) } else { NXDI_SNC_K(float) }
+#undef NXDI_SNC_K
+#undef NXDI_SNC
+    return;
+  }
   const int threads = p.W >= 1024 ? 256 : 128;
   if (out_lp) stream_norm_conv_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(p);
   else stream_norm_conv_kernel<float><<<grid, threads, 0, st>>>(p);

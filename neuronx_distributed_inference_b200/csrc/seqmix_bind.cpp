@@ -494,8 +494,8 @@ std::tuple<at::Tensor, at::Tensor> stream_norm_conv(const at::Tensor& x, const O
   check_i32(ctx, B, "ctx_len");
   check_i32(qlen, B, "q_len");
   c10::cuda::CUDAGuard guard(x.device());
-  auto s = at::zeros_like(x);                                                        // rows past q_len stay zero
-  auto out = at::zeros(x.sizes(), x.options().dtype(out_lp ? at::kBFloat16 : at::kFloat));
+  auto s = at::empty_like(x);                                                        // the kernel writes rows past q_len as zeros
+  auto out = at::empty(x.sizes(), x.options().dtype(out_lp ? at::kBFloat16 : at::kFloat));
   a.x = x.data_ptr<float>(); a.w = w.data_ptr<float>();
   a.ctx_len = ctx.data_ptr<int>(); a.q_len = qlen.data_ptr<int>();
   a.s = s.data_ptr<float>(); a.out = out.data_ptr();
