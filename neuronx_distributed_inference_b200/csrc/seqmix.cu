@@ -273,7 +273,8 @@ __global__ void __launch_bounds__(SPLIT ? 1024 : ATT_WARPS * 32) paged_window_at
   const int D = p.D, Dv = p.Dv, g = h / (p.Hq / p.G);
   float* qs = smem + warp * D;
   const T* qrow = (const T*)p.q + qi * D;
-  for (int d = lane; d < D; d += 32) qs[d] = ldf(qrow + d) * p.scale;
+  const float qscale = p.head_scale ? p.scale * p.head_scale[h] : p.scale;
+  for (int d = lane; d < D; d += 32) qs[d] = ldf(qrow + d) * qscale;
   __syncwarp();
   const int pos = p.ctx_len[b] + t;
   // visible keys: a window that ends at the query, or the query's chunk up to the query
@@ -451,6 +452,7 @@ __global__ void __launch_bounds__(128, (D + DV <= 256) ? 3 : 2) paged_window_att
   const int lo = p.chunk > 0 ? (p_first / p.chunk) * p.chunk : (p.window > 0 ? max(p_first - p.window + 1, 0) : 0);
   const int nA = p.window > 0 ? min(p.keep_first, lo) : 0;
   const float slope = p.slopes ? p.slopes[h] : 0.f;
+  const float hscale = p.head_scale ? p.scale * p.head_scale[h] : p.scale;
   const int* table = p.block_table + (long long)b * p.max_blocks;
   const __nv_bfloat16* kc = (const __nv_bfloat16*)p.k_cache;
   const __nv_bfloat16* vc = (const __nv_bfloat16*)p.v_cache;
@@ -521,7 +523,7 @@ __global__ void __launch_bounds__(128, (D + DV <= 256) ? 3 : 2) paged_window_att
       for (int nt = 0; nt < MMA_KT / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          float v = sc[nt][e] * p.scale;
+          float v = sc[nt][e] * hscale;
           if (p.softcap > 0.f) v = p.softcap * tanh_fast(v * inv_cap);
           const int j = j0 + nt * 8 + tig * 2 + (e & 1);
           const int pos = (e < 2) ? pos0 : pos1;
@@ -1289,6 +1291,7 @@ __device__ __forceinline__ float unary_apply(int act, float v) {
     case 3: return v / (1.f + expf(-v));
     case 4: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
     case 5: return 1.f / (1.f + expf(-v));
+    case 6: return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
     default: return v;
   }
 }
@@ -1335,6 +1338,683 @@ __global__ void __launch_bounds__(256) act_vec_kernel(const T* __restrict__ x, c
     o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
   }
   *reinterpret_cast<uint4*>(out + i * V) = o;
+}
+
+
+// ---- sandwich-norm stream update: y = sa f(a) + sb f(b); s = x + mult ls norm(y) post_w; h = norm(s) next_w ------------------------
+// One block per row; the row lives in shared memory (y, then s), so the centred second moments are true two-pass sums.
+template <typename TY, typename TH>
+__global__ void __launch_bounds__(256) stream_sandwich_norm_kernel(SandwichParams p) {
+  extern __shared__ float rowbuf[];      // [W]
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int W = p.W;
+  const float inv_w = 1.f / (float)W;
+  const float* xr = p.x + row * W;
+  float* so = p.s + row * W;
+  if (p.a) {
+    const TY* ar = (const TY*)p.a + row * W;
+    const TY* br = p.b ? (const TY*)p.b + row * W : nullptr;
+    float ra = 1.f, rb = 1.f;
+    if (p.a_w || (br && p.b_w)) {
+      float sa = 0.f, sb = 0.f;
+      for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float va = ldf(ar + c);
+        sa += va * va;
+        if (br) { const float vb = ldf(br + c); sb += vb * vb; }
+      }
+      if (p.a_w) ra = 1.f / sqrtf(block_sum(sa, red) * inv_w + p.eps);
+      if (br && p.b_w) rb = 1.f / sqrtf(block_sum(sb, red) * inv_w + p.eps);
+    }
+    float sum = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      float y = p.a_scale * (p.a_w ? ldf(ar + c) * ra * p.a_w[c] : ldf(ar + c));
+      if (br) y += p.b_scale * (p.b_w ? ldf(br + c) * rb * p.b_w[c] : ldf(br + c));
+      rowbuf[c] = y;
+      sum += y;
+    }
+    const float mean = p.center ? block_sum(sum, red) * inv_w : 0.f;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = rowbuf[c] - mean; sq += d * d; }
+    const float r = 1.f / sqrtf(block_sum(sq, red) * inv_w + p.eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+      float y = (rowbuf[c] - mean) * r;
+      if (p.post_w) y *= p.post_w[c];
+      if (p.ls) y *= p.ls[c];
+      const float s = xr[c] + p.mult * y;
+      so[c] = s;
+      rowbuf[c] = s;
+    }
+  } else {
+    for (int c = threadIdx.x; c < W; c += blockDim.x) { const float s = xr[c]; so[c] = s; rowbuf[c] = s; }
+  }
+  if (!p.h) return;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) sum += rowbuf[c];      // a thread re-reads only what it wrote itself
+  const float mean = p.center ? block_sum(sum, red) * inv_w : 0.f;
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) { const float d = rowbuf[c] - mean; sq += d * d; }
+  const float r = 1.f / sqrtf(block_sum(sq, red) * inv_w + p.eps);
+  TH* ho = (TH*)p.h + row * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) stf(ho + c, (rowbuf[c] - mean) * r * p.next_w[c]);
+}
+
+
+// The same with four values per thread and access: rows whose width is a multiple of 4 and at most 4 * 256 * NCH; the row stays in
+// registers from the first load to the last store (y, then s), every input is read once.
+__device__ __forceinline__ float sum4(float4 v) { return (v.x + v.y) + (v.z + v.w); }
+__device__ __forceinline__ float sq4(float4 v) { return v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+
+template <typename TY, typename TH, int NCH>
+__global__ void __launch_bounds__(256) stream_sandwich_norm_vec_kernel(SandwichParams p) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int W = p.W;
+  const float inv_w = 1.f / (float)W;
+  const float* xr = p.x + row * W;
+  float* so = p.s + row * W;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f), one = make_float4(1.f, 1.f, 1.f, 1.f);
+  float4 v[NCH];
+  if (p.a) {
+    const TY* ar = (const TY*)p.a + row * W;
+    const TY* br = p.b ? (const TY*)p.b + row * W : nullptr;
+    float4 bv[NCH];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 256 + threadIdx.x) * 4;
+      const bool in = c < W;
+      v[ch] = in ? ld4(ar + c) : zero;
+      bv[ch] = (in && br) ? ld4(br + c) : zero;
+      sa += sq4(v[ch]);
+      sb += sq4(bv[ch]);
+    }
+    float ra = 1.f, rb = 1.f;
+    if (p.a_w) ra = 1.f / sqrtf(block_sum(sa, red) * inv_w + p.eps);
+    if (br && p.b_w) rb = 1.f / sqrtf(block_sum(sb, red) * inv_w + p.eps);
+    ra *= p.a_scale;
+    rb *= p.b_scale;
+    float sum = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 256 + threadIdx.x) * 4;
+      if (c >= W) continue;
+      const float4 wa = p.a_w ? ld4(p.a_w + c) : one;
+      float4 y = make_float4(v[ch].x * ra * wa.x, v[ch].y * ra * wa.y, v[ch].z * ra * wa.z, v[ch].w * ra * wa.w);
+      if (br) {
+        const float4 wb = p.b_w ? ld4(p.b_w + c) : one;
+        y.x += bv[ch].x * rb * wb.x; y.y += bv[ch].y * rb * wb.y; y.z += bv[ch].z * rb * wb.z; y.w += bv[ch].w * rb * wb.w;
+      }
+      v[ch] = y;
+      sum += sum4(y);
+    }
+    const float mean = p.center ? block_sum(sum, red) * inv_w : 0.f;
+    float sq = 0.f;
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 256 + threadIdx.x) * 4;
+      if (c >= W) continue;
+      v[ch] = make_float4(v[ch].x - mean, v[ch].y - mean, v[ch].z - mean, v[ch].w - mean);
+      sq += sq4(v[ch]);
+    }
+    const float r = p.mult / sqrtf(block_sum(sq, red) * inv_w + p.eps);
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 256 + threadIdx.x) * 4;
+      if (c >= W) continue;
+      float4 g = p.post_w ? ld4(p.post_w + c) : one;
+      if (p.ls) { const float4 l = ld4(p.ls + c); g.x *= l.x; g.y *= l.y; g.z *= l.z; g.w *= l.w; }
+      const float4 x = ld4(xr + c);
+      v[ch] = make_float4(x.x + v[ch].x * r * g.x, x.y + v[ch].y * r * g.y, x.z + v[ch].z * r * g.z, x.w + v[ch].w * r * g.w);
+      st4(so + c, v[ch]);
+    }
+  } else {
+#pragma unroll
+    for (int ch = 0; ch < NCH; ++ch) {
+      const int c = (ch * 256 + threadIdx.x) * 4;
+      v[ch] = c < W ? ld4(xr + c) : zero;
+      if (c < W) st4(so + c, v[ch]);
+    }
+  }
+  if (!p.h) return;
+  float sum = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) sum += ((ch * 256 + threadIdx.x) * 4 < W) ? sum4(v[ch]) : 0.f;
+  const float mean = p.center ? block_sum(sum, red) * inv_w : 0.f;
+  float sq = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    if ((ch * 256 + threadIdx.x) * 4 >= W) continue;
+    v[ch] = make_float4(v[ch].x - mean, v[ch].y - mean, v[ch].z - mean, v[ch].w - mean);
+    sq += sq4(v[ch]);
+  }
+  const float r = 1.f / sqrtf(block_sum(sq, red) * inv_w + p.eps);
+  TH* ho = (TH*)p.h + row * W;
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c = (ch * 256 + threadIdx.x) * 4;
+    if (c >= W) continue;
+    const float4 g = ld4(p.next_w + c);
+    st4(ho + c, make_float4(v[ch].x * r * g.x, v[ch].y * r * g.y, v[ch].z * r * g.z, v[ch].w * r * g.w));
+  }
+}
+
+// ---- per-head q / k norm + rotate-half rotation + paged cache write -------------------------------------------------------------------
+// Block = one token, 8 warps; a warp takes heads warp, warp + 8, ... of the n_q + n_kv heads; lane l holds channels l, l + 32, ...
+constexpr int HNR_WARPS = 8;
+constexpr int HNR_CPL = 8;               // channels per lane: head sizes up to 256
+template <typename T>
+__global__ void __launch_bounds__(HNR_WARPS * 32) head_norm_rope_append_kernel(HeadNormRopeParams p) {
+  __shared__ float sh[HNR_WARPS][HNR_CPL * 32];
+  const int b = blockIdx.y, t = blockIdx.x;
+  if (t >= p.q_len[b]) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int D = p.D, Dv = p.Dv, R = p.R, half = R >> 1;
+  const long long tok = (long long)b * p.T + t;
+  const T* row = (const T*)p.p + (long long)b * p.p_sb + (long long)t * p.p_st;
+  const float* cs = p.cos ? p.cos + tok * half : nullptr;
+  const float* sn = p.sin ? p.sin + tok * half : nullptr;
+  const int pos = p.ctx_len[b] + t;
+  const long long slot = (long long)p.block_table[(long long)b * p.max_blocks + pos / p.page] * p.page + pos % p.page;
+  const int Cq = p.n_q * D, Ck = p.n_kv * D;
+  float* mine = sh[warp];
+  for (int hh = warp; hh < p.n_q + p.n_kv; hh += HNR_WARPS) {
+    const bool isq = hh < p.n_q;
+    const int g = isq ? hh : hh - p.n_q;
+    const T* src = row + (isq ? (long long)hh * D : (long long)Cq + (long long)g * D);
+    const float* nw = isq ? p.q_w : p.k_w;
+    float x[HNR_CPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < HNR_CPL; ++i) {
+      const int d = lane + 32 * i;
+      x[i] = d < D ? ldf(src + d) : 0.f;
+      ss += x[i] * x[i];
+    }
+    if (!isq && p.value_from_key) {          // the raw key doubles as the value
+      T* vo = (T*)p.v_cache + (slot * p.n_kv + g) * Dv;
+#pragma unroll
+      for (int i = 0; i < HNR_CPL; ++i) { const int d = lane + 32 * i; if (d < Dv) stf(vo + d, x[i]); }
+    }
+    if (p.norm_at == 1) {
+      const float r = 1.f / sqrtf(warp_sum(ss) / (float)D + p.eps);
+#pragma unroll
+      for (int i = 0; i < HNR_CPL; ++i) { const int d = lane + 32 * i; x[i] = d < D ? x[i] * r * (nw ? nw[d] : 1.f) : 0.f; }
+    }
+    if (cs) {
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < HNR_CPL; ++i) { const int d = lane + 32 * i; if (d < R) mine[d] = x[i]; }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < HNR_CPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < R) {
+          const int f = d < half ? d : d - half;
+          const float co = cs[f], si = sn[f], other = mine[d < half ? d + half : d - half];
+          x[i] = d < half ? x[i] * co - other * si : x[i] * co + other * si;
+        }
+      }
+    }
+    if (p.norm_at == 2) {
+      float s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < HNR_CPL; ++i) s2 += x[i] * x[i];
+      const float r = 1.f / sqrtf(warp_sum(s2) / (float)D + p.eps);
+#pragma unroll
+      for (int i = 0; i < HNR_CPL; ++i) { const int d = lane + 32 * i; x[i] = d < D ? x[i] * r * (nw ? nw[d] : 1.f) : 0.f; }
+    }
+    T* dst = isq ? (T*)p.q_out + (tok * p.n_q + hh) * D : (T*)p.k_cache + (slot * p.n_kv + g) * D;
+#pragma unroll
+    for (int i = 0; i < HNR_CPL; ++i) { const int d = lane + 32 * i; if (d < D) stf(dst + d, x[i]); }
+  }
+  if (!p.value_from_key) {
+    const T* vs = row + Cq + Ck;
+    T* vo = (T*)p.v_cache + slot * p.n_kv * Dv;
+    for (int c = threadIdx.x; c < p.n_kv * Dv; c += blockDim.x) vo[c] = vs[c];
+  }
+}
+
+
+// Head sizes of 32 * VPL (64, 128, 256) with rotated halves that are multiples of VPL: lane l holds channels [l VPL, (l + 1) VPL) as ONE
+// vector access, and the rotation partner of a channel sits in the same register of lane l +- (R / 2) / VPL: a shuffle, no shared memory.
+template <typename T, int VPL>
+__device__ __forceinline__ void ld_vpl(const T* p, float* x) {
+  if constexpr (std::is_same<T, float>::value) {
+#pragma unroll
+    for (int e = 0; e < VPL; e += 2) { const float2 v = *reinterpret_cast<const float2*>(p + e); x[e] = v.x; x[e + 1] = v.y; }
+  } else if constexpr (VPL == 2) {
+    const float2 v = ld2(p); x[0] = v.x; x[1] = v.y;
+  } else if constexpr (VPL == 4) {
+    const float4 v = ld4(p); x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+  } else {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    x[0] = bf16lo(r.x); x[1] = bf16hi(r.x); x[2] = bf16lo(r.y); x[3] = bf16hi(r.y); x[4] = bf16lo(r.z); x[5] = bf16hi(r.z); x[6] = bf16lo(r.w); x[7] = bf16hi(r.w);
+  }
+}
+template <typename T, int VPL>
+__device__ __forceinline__ void st_vpl(T* p, const float* x) {
+  if constexpr (std::is_same<T, float>::value) {
+#pragma unroll
+    for (int e = 0; e < VPL; e += 2) *reinterpret_cast<float2*>(p + e) = make_float2(x[e], x[e + 1]);
+  } else if constexpr (VPL == 2) {
+    st2(p, x[0], x[1]);
+  } else if constexpr (VPL == 4) {
+    st4(p, make_float4(x[0], x[1], x[2], x[3]));
+  } else {
+    *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+  }
+}
+
+template <typename T, int VPL>
+__global__ void __launch_bounds__(HNR_WARPS * 32) head_norm_rope_append_lane_kernel(HeadNormRopeParams p) {
+  const int b = blockIdx.y, t = blockIdx.x;
+  if (t >= p.q_len[b]) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int D = 32 * VPL;
+  const int Dv = p.Dv, R = p.R, half = R >> 1, d0 = lane * VPL;
+  const long long tok = (long long)b * p.T + t;
+  const T* row = (const T*)p.p + (long long)b * p.p_sb + (long long)t * p.p_st;
+  const int pos = p.ctx_len[b] + t;
+  const long long slot = (long long)p.block_table[(long long)b * p.max_blocks + pos / p.page] * p.page + pos % p.page;
+  const int Cq = p.n_q * D, Ck = p.n_kv * D;
+  // this lane's cos / sin (the same for every head of the token) and where its rotation partner sits
+  const bool rot = p.cos && d0 < R, low = d0 < half;
+  const int f0 = low ? d0 : d0 - half, partner = low ? lane + half / VPL : lane - half / VPL;
+  float co[VPL], si[VPL];
+#pragma unroll
+  for (int e = 0; e < VPL; ++e) {
+    co[e] = rot ? p.cos[tok * half + f0 + e] : 1.f;
+    si[e] = rot ? p.sin[tok * half + f0 + e] : 0.f;
+    if (low) si[e] = -si[e];          // x_lo' = x_lo c - x_hi s, x_hi' = x_hi c + x_lo s: the low half takes the minus sign
+  }
+  for (int hh = warp; hh < p.n_q + p.n_kv; hh += HNR_WARPS) {
+    const bool isq = hh < p.n_q;
+    const int g = isq ? hh : hh - p.n_q;
+    const T* src = row + (isq ? (long long)hh * D : (long long)Cq + (long long)g * D) + d0;
+    const float* nw = isq ? p.q_w : p.k_w;
+    float x[VPL];
+    ld_vpl<T, VPL>(src, x);
+    if (!isq && p.value_from_key) st_vpl<T, VPL>((T*)p.v_cache + (slot * p.n_kv + g) * Dv + d0, x);      // the raw key doubles as the value
+    if (p.norm_at == 1) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) ss += x[e] * x[e];
+      const float r = 1.f / sqrtf(warp_sum(ss) / (float)D + p.eps);
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) x[e] = x[e] * r * (nw ? nw[d0 + e] : 1.f);
+    }
+    if (p.cos) {
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) {
+        const float other = __shfl_sync(0xffffffffu, x[e], partner & 31);
+        x[e] = x[e] * co[e] + other * si[e];
+      }
+    }
+    if (p.norm_at == 2) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) ss += x[e] * x[e];
+      const float r = 1.f / sqrtf(warp_sum(ss) / (float)D + p.eps);
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) x[e] = x[e] * r * (nw ? nw[d0 + e] : 1.f);
+    }
+    st_vpl<T, VPL>((isq ? (T*)p.q_out + (tok * p.n_q + hh) * D : (T*)p.k_cache + (slot * p.n_kv + g) * D) + d0, x);
+  }
+  if (!p.value_from_key) {
+    const T* vs = row + Cq + Ck;
+    T* vo = (T*)p.v_cache + slot * p.n_kv * Dv;
+    constexpr int VN = Vec<T>::N;
+    const int n = p.n_kv * Dv;
+    if (n % VN == 0 && (((uintptr_t)vs | (uintptr_t)vo) & 15) == 0) {
+      for (int c = threadIdx.x * VN; c < n; c += blockDim.x * VN) *reinterpret_cast<uint4*>(vo + c) = *reinterpret_cast<const uint4*>(vs + c);
+    } else {
+      for (int c = threadIdx.x; c < n; c += blockDim.x) vo[c] = vs[c];
+    }
+  }
+}
+
+// ---- gated delta rule with a carried state -------------------------------------------------------------------------------------------
+// Block = one (row, head, 16 value channels); 8 lanes split the key axis of a state column and hold their share in registers.  The
+// columns of S are independent: with the OLD column s, r = g (s . k), u = beta (v - r), o = g (s . q) + u (k . q), s <- g s + k u, so both
+// dot products of a step run on the old state and share one lane reduction.  Time runs in batches of 16 steps: raw q / k of batch
+// r + 1 are fetched into registers while batch r is computed out of shared memory; their unit norms, k . q, beta and the decay are
+// formed once per batch and folded into per-step scalars.
+constexpr int DLT_PT = 16, DLT_NS = 8, DLT_TT = 16, DLT_THREADS = DLT_PT * DLT_NS;
+
+template <typename T, int NB>
+__global__ void __launch_bounds__(DLT_THREADS, NB == 1 ? 4 : 2) gated_delta_scan_kernel(DeltaScanParams p) {
+  extern __shared__ float sm[];
+  constexpr int DPT = 16 * NB;             // key channels per lane: d = ns * DPT + i
+  constexpr int DP = 160 * NB;             // padded staged row: 4 floats after every 16
+  const int D = p.D, Dv = p.Dv;
+  float* qs = sm;                          // [TT][DP] raw q, zero past D
+  float* ks = qs + DLT_TT * DP;            // [TT][DP] raw k
+  float* vs = ks + DLT_TT * DP;            // [TT][PT]
+  float* os = vs + DLT_TT * DLT_PT;        // [TT][PT]
+  float* cg = os + DLT_TT * DLT_PT;        // [TT] decay
+  float* cb = cg + DLT_TT;                 // [TT] beta
+  float* cq = cb + DLT_TT;                 // [TT] 1 / |q| * D^-1/2
+  float* ck = cq + DLT_TT;                 // [TT] 1 / |k|
+  float* ckq = ck + DLT_TT;                // [TT] unit k . scaled unit q
+  const int b = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * DLT_PT;
+  const int n_tok = p.q_len[b];
+  if (n_tok <= 0) return;
+  const int tid = threadIdx.x, pl = tid / DLT_NS, ns = tid % DLT_NS, warp = tid >> 5, lane = tid & 31;
+  const int pc = p0 + pl;
+  const bool pok = pc < Dv;
+  const int gq = h / (p.nh / p.n_qk);
+  const int Cq = p.n_qk * D, C = 2 * Cq + p.nh * Dv;
+  float* Sg = p.state + ((long long)p.lines[b] * p.nh + h) * D * Dv;
+  float S[DPT];
+  const bool has_ctx = p.ctx_len[b] > 0;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = ns * DPT + i;
+    S[i] = (has_ctx && pok && d < D) ? Sg[(long long)d * Dv + pc] : 0.f;
+  }
+  const float negA = -expf(p.A_log[h]), dtb = p.dt_bias[h], qmul = 1.f / sqrtf((float)D);
+  const float* xrow = p.qkv + (long long)b * p.T * C;
+  const T* bp = (const T*)p.beta_raw + (long long)b * p.beta_sb + h;
+  const T* ap = (const T*)p.a_raw + (long long)b * p.a_sb + h;
+  float rq[DPT], rk[DPT], rv[2], rbeta = 0.f, ra = 0.f;
+  auto fetch = [&](int t0) {
+    const int tt = min(DLT_TT, n_tok - t0);
+#pragma unroll
+    for (int t = 0; t < DLT_TT; ++t)
+#pragma unroll
+      for (int k = 0; k < NB; ++k) {
+        const int d = tid + DLT_THREADS * k;
+        const bool ok = t < tt && d < D;
+        const float* r = xrow + (long long)(t0 + t) * C + gq * D + d;
+        rq[t * NB + k] = ok ? r[0] : 0.f;
+        rk[t * NB + k] = ok ? r[Cq] : 0.f;
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int i = tid + DLT_THREADS * k, t = i / DLT_PT, c = p0 + i % DLT_PT;
+      rv[k] = (t < tt && c < Dv) ? xrow[(long long)(t0 + t) * C + 2 * Cq + h * Dv + c] : 0.f;
+    }
+    rbeta = tid < tt ? ldf(bp + (long long)(t0 + tid) * p.beta_st) : 0.f;
+    ra = tid < tt ? ldf(ap + (long long)(t0 + tid) * p.a_st) : 0.f;
+  };
+  fetch(0);
+  for (int t0 = 0; t0 < n_tok; t0 += DLT_TT) {
+    const int tt = min(DLT_TT, n_tok - t0);
+    __syncthreads();                      // the readers of the previous batch are done with the tiles
+#pragma unroll
+    for (int t = 0; t < DLT_TT; ++t)
+#pragma unroll
+      for (int k = 0; k < NB; ++k) {
+        const int d = tid + DLT_THREADS * k, at = t * DP + d + (d >> 4) * 4;
+        qs[at] = rq[t * NB + k];
+        ks[at] = rk[t * NB + k];
+      }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) vs[tid + DLT_THREADS * k] = rv[k];
+    if (tid < DLT_TT) {
+      const float v = ra + dtb;
+      const float sp = v > 20.f ? v : log1pf(expf(v));
+      cg[tid] = expf(negA * sp);
+      cb[tid] = sigmoidf_acc(rbeta);
+    }
+    __syncthreads();
+    // unit norms and k . q of the batch: warp w takes steps w, w + 4, ...
+    for (int t = warp; t < DLT_TT; t += DLT_THREADS / 32) {
+      float qq = 0.f, kk = 0.f, kq = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const int at = t * DP + d + (d >> 4) * 4;
+        const float a = qs[at], c = ks[at];
+        qq += a * a; kk += c * c; kq += a * c;
+      }
+      qq = warp_sum(qq); kk = warp_sum(kk); kq = warp_sum(kq);
+      if (lane == 0) {
+        const float iq = qmul / sqrtf(qq + p.unit_eps), ik = 1.f / sqrtf(kk + p.unit_eps);
+        cq[t] = iq; ck[t] = ik; ckq[t] = kq * iq * ik;
+      }
+    }
+    __syncthreads();
+    if (t0 + DLT_TT < n_tok) fetch(t0 + DLT_TT);      // in flight while the current steps are computed
+#pragma unroll 2
+    for (int t = 0; t < tt; ++t) {
+      const float4* Kt = reinterpret_cast<const float4*>(ks + t * DP) + ns * (DPT * 5 / 16);
+      const float4* Qt = reinterpret_cast<const float4*>(qs + t * DP) + ns * (DPT * 5 / 16);
+      float4 kv[DPT / 4];
+      float k0 = 0.f, k1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll
+      for (int q = 0; q < DPT / 4; ++q) {
+        kv[q] = Kt[q + (q >> 2)];
+        const float4 qv = Qt[q + (q >> 2)];
+        k0 += S[4 * q] * kv[q].x + S[4 * q + 2] * kv[q].z;
+        k1 += S[4 * q + 1] * kv[q].y + S[4 * q + 3] * kv[q].w;
+        q0 += S[4 * q] * qv.x + S[4 * q + 2] * qv.z;
+        q1 += S[4 * q + 1] * qv.y + S[4 * q + 3] * qv.w;
+      }
+      float sk = k0 + k1, sq = q0 + q1;
+#pragma unroll
+      for (int o = DLT_NS / 2; o > 0; o >>= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      }
+      const float g = cg[t], ikn = ck[t];
+      const float u = cb[t] * (vs[t * DLT_PT + pl] - g * ikn * sk);
+      const float ku = ikn * u;
+#pragma unroll
+      for (int q = 0; q < DPT / 4; ++q) {
+        S[4 * q] = g * S[4 * q] + ku * kv[q].x;
+        S[4 * q + 1] = g * S[4 * q + 1] + ku * kv[q].y;
+        S[4 * q + 2] = g * S[4 * q + 2] + ku * kv[q].z;
+        S[4 * q + 3] = g * S[4 * q + 3] + ku * kv[q].w;
+      }
+      if (ns == 0) os[t * DLT_PT + pl] = g * cq[t] * sq + u * ckq[t];
+    }
+    __syncthreads();
+    for (int i = tid; i < tt * DLT_PT; i += DLT_THREADS) {
+      const int t = i / DLT_PT, c = p0 + i % DLT_PT;
+      if (c < Dv) p.o[((long long)b * p.T + t0 + t) * p.nh * Dv + h * Dv + c] = os[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = ns * DPT + i;
+    if (pok && d < D) Sg[(long long)d * Dv + pc] = S[i];
+  }
+}
+
+
+// The same recurrence with TWO state columns per thread (8 lanes x DPT key channels each): the k / q values a thread reads from
+// shared memory serve both columns, which halves the shared-memory traffic per state element (the recurrent form is bound by it: every
+// column needs the whole k and q of every step), and q / k / v of the next 16 steps are copied straight into a second shared-memory
+// stage with cp.async, so no registers are spent on prefetching.  Thread (t, part) forms the unit norms and k . q of step t from a
+// quarter of the row (one short lane reduction instead of a warp-wide one); the per-step scalars are folded into one float4 and one
+// float2.  Taken when every 16-byte copy is aligned (row width, head size and value size multiples of 4).
+constexpr int DL2_PT = 16, DL2_TT = 16, DL2_NS = 8, DL2_CPT = 2, DL2_THREADS = (DL2_PT / DL2_CPT) * DL2_NS;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool on) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  const int n = on ? 16 : 0;          // 0 bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n));
+}
+
+template <typename T, int DPT>           // DPT key channels per lane: 16 (D <= 128) or 32 (D <= 256)
+__global__ void __launch_bounds__(DL2_THREADS) gated_delta_scan_wide_kernel(DeltaScanParams p) {
+  extern __shared__ __align__(16) float sm2[];
+  constexpr int THREADS = DL2_THREADS, NS = DL2_NS, CPT = DL2_CPT;
+  constexpr int DPAD = DPT * NS;                           // staged key channels (zero past D)
+  constexpr int DP = DPAD + (DPAD / 16) * 4 + 4;           // row stride: 4 floats after every 16, 4 more so that rows start 4 banks apart
+  constexpr int STAGE = 2 * DL2_TT * DP + DL2_TT * DL2_PT; // q rows, k rows, v tile
+  constexpr int QPART = DPAD / 4;                          // channels per thread in the norm phase (4 threads per step)
+  float* stage0 = sm2;
+  float4* coefA = reinterpret_cast<float4*>(sm2 + 2 * STAGE);           // [TT] decay, decay / |k|, beta, 1 / |k|
+  float2* coefB = reinterpret_cast<float2*>(coefA + DL2_TT);            // [TT] decay D^-1/2 / |q|, unit k . scaled unit q
+  float* os = reinterpret_cast<float*>(coefB + DL2_TT);                 // [TT][PT]
+  const int D = p.D, Dv = p.Dv;
+  const int b = blockIdx.z, h = blockIdx.y, p0 = blockIdx.x * DL2_PT;
+  const int n_tok = p.q_len[b];
+  if (n_tok <= 0) return;
+  const int tid = threadIdx.x, pl = tid / NS, ns = tid % NS;            // pl: this thread's pair of columns
+  const int nt = tid / 4, npart = tid % 4;                              // norm phase: step and quarter of the row
+  const int gq = h / (p.nh / p.n_qk);
+  const int Cq = p.n_qk * D, C = 2 * Cq + p.nh * Dv;
+  float* Sg = p.state + ((long long)p.lines[b] * p.nh + h) * D * Dv;
+  float S[CPT][DPT];
+  const bool has_ctx = p.ctx_len[b] > 0;
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = ns * DPT + i, pc = p0 + pl * CPT + c;
+      S[c][i] = (has_ctx && pc < Dv && d < D) ? Sg[(long long)d * Dv + pc] : 0.f;
+    }
+  const float negA = -expf(p.A_log[h]), dtb = p.dt_bias[h], qmul = 1.f / sqrtf((float)D);
+  const float* xrow = p.qkv + (long long)b * p.T * C;
+  const T* bp = (const T*)p.beta_raw + (long long)b * p.beta_sb + h;
+  const T* ap = (const T*)p.a_raw + (long long)b * p.a_sb + h;
+  float rbeta = 0.f, ra = 0.f;           // raw beta / a of step `nt` of the batch in flight (thread (nt, 0) turns them into coefficients)
+  auto issue = [&](int t0, int st) {
+    const int tt = min(DL2_TT, n_tok - t0);
+    float* qd = stage0 + st * STAGE;
+    float* kd = qd + DL2_TT * DP;
+    float* vd = kd + DL2_TT * DP;
+    constexpr int CPR = DPAD / 4;          // 16-byte chunks per staged row
+    for (int c = tid; c < DL2_TT * CPR; c += THREADS) {
+      const int t = c / CPR, d = (c % CPR) * 4;
+      const bool on = t < tt && d < D;
+      const float* src = on ? xrow + (long long)(t0 + t) * C + gq * D + d : xrow;
+      const int at = t * DP + d + (d >> 4) * 4;
+      cp_async16(qd + at, src, on);
+      cp_async16(kd + at, on ? src + Cq : xrow, on);
+    }
+    for (int c = tid; c < DL2_TT * (DL2_PT / 4); c += THREADS) {
+      const int t = c / (DL2_PT / 4), col = (c % (DL2_PT / 4)) * 4;
+      const bool on = t < tt && p0 + col < Dv;
+      cp_async16(vd + t * DL2_PT + col, on ? xrow + (long long)(t0 + t) * C + 2 * Cq + h * Dv + p0 + col : xrow, on);
+    }
+    asm volatile("cp.async.commit_group;");
+    const bool mine = npart == 0 && nt < tt;
+    rbeta = mine ? ldf(bp + (long long)(t0 + nt) * p.beta_st) : 0.f;
+    ra = mine ? ldf(ap + (long long)(t0 + nt) * p.a_st) : 0.f;
+  };
+  issue(0, 0);
+  int st = 0;
+  for (int t0 = 0; t0 < n_tok; t0 += DL2_TT, st ^= 1) {
+    const int tt = min(DL2_TT, n_tok - t0);
+    asm volatile("cp.async.wait_group 0;");
+    __syncthreads();                      // this batch has landed; everyone is done with the other stage, the coefficients and the outputs
+    const float* qs = stage0 + st * STAGE;
+    const float* ks = qs + DL2_TT * DP;
+    const float* vs = ks + DL2_TT * DP;
+    {
+      // thread (nt, npart): a quarter of step nt's raw q and k
+      const float4* Kt = reinterpret_cast<const float4*>(ks + nt * DP) + npart * (QPART * 5 / 16);
+      const float4* Qt = reinterpret_cast<const float4*>(qs + nt * DP) + npart * (QPART * 5 / 16);
+      float qq = 0.f, kk = 0.f, kq = 0.f;
+#pragma unroll
+      for (int q = 0; q < QPART / 4; ++q) {
+        const float4 a = Qt[q + (q >> 2)], c = Kt[q + (q >> 2)];
+        qq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        kk += c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w;
+        kq += a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w;
+      }
+#pragma unroll
+      for (int o = 2; o > 0; o >>= 1) {
+        qq += __shfl_xor_sync(0xffffffffu, qq, o);
+        kk += __shfl_xor_sync(0xffffffffu, kk, o);
+        kq += __shfl_xor_sync(0xffffffffu, kq, o);
+      }
+      if (npart == 0) {
+        const float v = ra + dtb;
+        const float sp = v > 20.f ? v : log1pf(expf(v));
+        const float g = expf(negA * sp), beta = sigmoidf_acc(rbeta);
+        const float iq = qmul / sqrtf(qq + p.unit_eps), ik = 1.f / sqrtf(kk + p.unit_eps);
+        coefA[nt] = make_float4(g, g * ik, beta, ik);
+        coefB[nt] = make_float2(g * iq, kq * iq * ik);
+      }
+    }
+    __syncthreads();
+    if (t0 + DL2_TT < n_tok) issue(t0 + DL2_TT, st ^ 1);      // lands while the current steps are computed
+#pragma unroll 2
+    for (int t = 0; t < tt; ++t) {
+      const float4* Kt = reinterpret_cast<const float4*>(ks + t * DP) + ns * (DPT * 5 / 16);
+      const float4* Qt = reinterpret_cast<const float4*>(qs + t * DP) + ns * (DPT * 5 / 16);
+      float4 kv[DPT / 4];
+      float sk[CPT], sq[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) sk[c] = sq[c] = 0.f;
+#pragma unroll
+      for (int q = 0; q < DPT / 4; ++q) {
+        kv[q] = Kt[q + (q >> 2)];
+        const float4 qv = Qt[q + (q >> 2)];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          sk[c] += (S[c][4 * q] * kv[q].x + S[c][4 * q + 2] * kv[q].z) + (S[c][4 * q + 1] * kv[q].y + S[c][4 * q + 3] * kv[q].w);
+          sq[c] += (S[c][4 * q] * qv.x + S[c][4 * q + 2] * qv.z) + (S[c][4 * q + 1] * qv.y + S[c][4 * q + 3] * qv.w);
+        }
+      }
+#pragma unroll
+      for (int o = NS / 2; o > 0; o >>= 1)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          sk[c] += __shfl_xor_sync(0xffffffffu, sk[c], o);
+          sq[c] += __shfl_xor_sync(0xffffffffu, sq[c], o);
+        }
+      const float4 cA = coefA[t];
+      const float2 cB = coefB[t];
+      const float g = cA.x;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) {
+        const float u = cA.z * (vs[t * DL2_PT + pl * CPT + c] - cA.y * sk[c]);
+        const float ku = cA.w * u;
+#pragma unroll
+        for (int q = 0; q < DPT / 4; ++q) {
+          S[c][4 * q] = g * S[c][4 * q] + ku * kv[q].x;
+          S[c][4 * q + 1] = g * S[c][4 * q + 1] + ku * kv[q].y;
+          S[c][4 * q + 2] = g * S[c][4 * q + 2] + ku * kv[q].z;
+          S[c][4 * q + 3] = g * S[c][4 * q + 3] + ku * kv[q].w;
+        }
+        if (ns == 0) os[t * DL2_PT + pl * CPT + c] = cB.x * sq[c] + u * cB.y;
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < tt * DL2_PT; i += THREADS) {
+      const int t = i / DL2_PT, c = p0 + i % DL2_PT;
+      if (c < Dv) p.o[((long long)b * p.T + t0 + t) * p.nh * Dv + h * Dv + c] = os[i];
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = ns * DPT + i, pc = p0 + pl * CPT + c;
+      if (pc < Dv && d < D) Sg[(long long)d * Dv + pc] = S[c][i];
+    }
+}
+
+// ---- per-head RMS norm with a shared weight, times an activated gate: one warp per (row, head) ------------------------------------------
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(128) head_rmsnorm_gate_kernel(const float* __restrict__ y, const float* __restrict__ w, const TG* __restrict__ gate,
+                                                                long long g_stride, TO* __restrict__ out, long long nrh, int H, int Dv, float eps,
+                                                                int act) {
+  const long long i = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (i >= nrh) return;
+  const int lane = threadIdx.x & 31, h = (int)(i % H);
+  const long long row = i / H;
+  const float* yr = y + i * Dv;
+  float v[SEQMIX_MAX_VDIM / 32], ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < SEQMIX_MAX_VDIM / 32; ++k) {
+    const int d = lane + 32 * k;
+    v[k] = d < Dv ? yr[d] : 0.f;
+    ss += v[k] * v[k];
+  }
+  const float r = 1.f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+  const TG* gr = gate + row * g_stride + (long long)h * Dv;
+  TO* orow = out + i * Dv;
+#pragma unroll
+  for (int k = 0; k < SEQMIX_MAX_VDIM / 32; ++k) {
+    const int d = lane + 32 * k;
+    if (d < Dv) stf(orow + d, v[k] * r * w[d] * unary_apply(act, ldf(gr + d)));
+  }
 }
 
 template <typename K>
@@ -1600,6 +2280,106 @@ void ssd_scan_launch(const SsdScanParams& p, bool lp, cudaStream_t st) {
     if (lp) go(ssd_scan_kernel<__nv_bfloat16, 1>); else go(ssd_scan_kernel<float, 1>);
   } else {
     if (lp) go(ssd_scan_kernel<__nv_bfloat16, 2>); else go(ssd_scan_kernel<float, 2>);
+  }
+}
+
+void stream_sandwich_norm_launch(const SandwichParams& p, bool y_lp, bool h_lp, cudaStream_t st) {
+  if (p.rows <= 0) return;
+  const size_t smem = sizeof(float) * (size_t)p.W;
+  const uintptr_t ptrs = (uintptr_t)p.x | (uintptr_t)p.a | (uintptr_t)p.b | (uintptr_t)p.a_w | (uintptr_t)p.b_w | (uintptr_t)p.post_w | (uintptr_t)p.ls |
+                         (uintptr_t)p.next_w | (uintptr_t)p.s | (uintptr_t)p.h;
+  if (p.W % 4 == 0 && p.W <= 8192 && (ptrs & 15) == 0) {
+    // the mixed-type instantiations (bf16 results into an fp32 norm and the reverse) stay on the scalar kernel
+    auto pick = [&](auto ty, auto th) {
+      using TY = decltype(ty);
+      using TH = decltype(th);
+      if (p.W <= 1024) stream_sandwich_norm_vec_kernel<TY, TH, 1><<<p.rows, 256, 0, st>>>(p);
+      else if (p.W <= 2048) stream_sandwich_norm_vec_kernel<TY, TH, 2><<<p.rows, 256, 0, st>>>(p);
+      else if (p.W <= 4096) stream_sandwich_norm_vec_kernel<TY, TH, 4><<<p.rows, 256, 0, st>>>(p);
+      else stream_sandwich_norm_vec_kernel<TY, TH, 8><<<p.rows, 256, 0, st>>>(p);
+    };
+    if (y_lp && h_lp) { pick(__nv_bfloat16{}, __nv_bfloat16{}); return; }
+    if (!y_lp && !h_lp) { pick(float{}, float{}); return; }
+  }
+  auto go = [&](auto kernel) {
+    opt_in_smem(kernel, smem);
+    kernel<<<p.rows, 256, smem, st>>>(p);
+  };
+  if (y_lp) {
+    if (h_lp) go(stream_sandwich_norm_kernel<__nv_bfloat16, __nv_bfloat16>); else go(stream_sandwich_norm_kernel<__nv_bfloat16, float>);
+  } else {
+    if (h_lp) go(stream_sandwich_norm_kernel<float, __nv_bfloat16>); else go(stream_sandwich_norm_kernel<float, float>);
+  }
+}
+
+void head_norm_rope_append_launch(const HeadNormRopeParams& p, bool lp, cudaStream_t st) {
+  if (p.B <= 0 || p.T <= 0) return;
+  dim3 grid(p.T, p.B);
+  const int vpl = p.D / 32;
+  const size_t esz = lp ? 2 : 4;
+  // one vector access per lane: head size 64 / 128 / 256, rotated halves in whole lanes, every row a multiple of the access size
+  const bool lanes = p.D % 32 == 0 && (vpl == 2 || vpl == 4 || vpl == 8) && (!p.cos || (p.R / 2) % vpl == 0) && (!p.value_from_key || p.Dv == p.D) &&
+                     ((uintptr_t)p.p % 16) == 0 && (p.p_sb * esz) % 16 == 0 && (p.p_st * esz) % 16 == 0;
+  if (lanes) {
+    auto go = [&](auto kernel) { kernel<<<grid, HNR_WARPS * 32, 0, st>>>(p); };
+    if (lp) {
+      if (vpl == 2) go(head_norm_rope_append_lane_kernel<__nv_bfloat16, 2>);
+      else if (vpl == 4) go(head_norm_rope_append_lane_kernel<__nv_bfloat16, 4>);
+      else go(head_norm_rope_append_lane_kernel<__nv_bfloat16, 8>);
+    } else {
+      if (vpl == 2) go(head_norm_rope_append_lane_kernel<float, 2>);
+      else if (vpl == 4) go(head_norm_rope_append_lane_kernel<float, 4>);
+      else go(head_norm_rope_append_lane_kernel<float, 8>);
+    }
+    return;
+  }
+  if (lp) head_norm_rope_append_kernel<__nv_bfloat16><<<grid, HNR_WARPS * 32, 0, st>>>(p);
+  else head_norm_rope_append_kernel<float><<<grid, HNR_WARPS * 32, 0, st>>>(p);
+}
+
+void gated_delta_scan_launch(const DeltaScanParams& p, bool lp, cudaStream_t st) {
+  if (p.B <= 0 || p.T <= 0) return;
+  const int nb = p.D <= 128 ? 1 : 2;
+  dim3 grid((p.Dv + DLT_PT - 1) / DLT_PT, p.nh, p.B);
+  const long long C = 2LL * p.n_qk * p.D + (long long)p.nh * p.Dv;
+  if (p.D % 4 == 0 && p.Dv % 4 == 0 && C % 4 == 0 && ((uintptr_t)p.qkv % 16) == 0) {
+    // every 16-byte copy of q / k / v rows is aligned: the two-stage kernel with two state columns per thread
+    const int dpad = 16 * nb * DL2_NS, dp = dpad + (dpad / 16) * 4 + 4;
+    const size_t smem2 = sizeof(float) * (size_t)(2 * (2 * DL2_TT * dp + DL2_TT * DL2_PT) + 4 * DL2_TT + 2 * DL2_TT + DL2_TT * DL2_PT);
+    auto go2 = [&](auto kernel) {
+      opt_in_smem(kernel, smem2);
+      kernel<<<grid, DL2_THREADS, smem2, st>>>(p);
+    };
+    if (nb == 1) {
+      if (lp) go2(gated_delta_scan_wide_kernel<__nv_bfloat16, 16>); else go2(gated_delta_scan_wide_kernel<float, 16>);
+    } else {
+      if (lp) go2(gated_delta_scan_wide_kernel<__nv_bfloat16, 32>); else go2(gated_delta_scan_wide_kernel<float, 32>);
+    }
+    return;
+  }
+  const size_t smem = sizeof(float) * (size_t)(2 * DLT_TT * 160 * nb + 2 * DLT_TT * DLT_PT + 5 * DLT_TT);
+  auto go = [&](auto kernel) {
+    opt_in_smem(kernel, smem);
+    kernel<<<grid, DLT_THREADS, smem, st>>>(p);
+  };
+  if (nb == 1) {
+    if (lp) go(gated_delta_scan_kernel<__nv_bfloat16, 1>); else go(gated_delta_scan_kernel<float, 1>);
+  } else {
+    if (lp) go(gated_delta_scan_kernel<__nv_bfloat16, 2>); else go(gated_delta_scan_kernel<float, 2>);
+  }
+}
+
+void head_rmsnorm_gate_launch(const float* y, const float* w, const void* gate, long long g_stride, void* out, long long rows, int H, int Dv,
+                              float eps, int act, bool gate_lp, bool out_lp, cudaStream_t st) {
+  const long long nrh = rows * H;
+  if (nrh <= 0) return;
+  const unsigned grid = (unsigned)((nrh + 3) / 4);
+  if (gate_lp) {
+    if (out_lp) head_rmsnorm_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, 0, st>>>(y, w, (const __nv_bfloat16*)gate, g_stride, (__nv_bfloat16*)out, nrh, H, Dv, eps, act);
+    else head_rmsnorm_gate_kernel<__nv_bfloat16, float><<<grid, 128, 0, st>>>(y, w, (const __nv_bfloat16*)gate, g_stride, (float*)out, nrh, H, Dv, eps, act);
+  } else {
+    if (out_lp) head_rmsnorm_gate_kernel<float, __nv_bfloat16><<<grid, 128, 0, st>>>(y, w, (const float*)gate, g_stride, (__nv_bfloat16*)out, nrh, H, Dv, eps, act);
+    else head_rmsnorm_gate_kernel<float, float><<<grid, 128, 0, st>>>(y, w, (const float*)gate, g_stride, (float*)out, nrh, H, Dv, eps, act);
   }
 }
 

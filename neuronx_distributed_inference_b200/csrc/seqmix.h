@@ -63,7 +63,7 @@ void identity_expert_add_launch(void* y, const void* x, const float* topk_w, con
 // x [rows, H, D] *= sigmoid(gate[row, h]) in place; gate rows are g_stride elements apart; D a multiple of 16 bytes
 void head_gate_mul_launch(void* x, const void* gate, long long g_stride, long long rows, int H, int D, bool lp, cudaStream_t st);
 
-// act codes: 1 relu, 2 relu^2, 3 silu, 4 tanh-gelu, 5 sigmoid.  on_other: out = gate * act(other) instead of act(gate) * other.
+// act codes: 1 relu, 2 relu^2, 3 silu, 4 tanh-gelu, 5 sigmoid, 6 erf-gelu.  on_other: out = gate * act(other) instead of act(gate) * other.
 // g_stride: elements between rows of `gate` (C when dense).
 void gated_act_mul_launch(const void* gate, long long g_stride, const void* other, long long o_stride, void* out, long long rows, int C, int act,
                           bool on_other, bool lp, cudaStream_t st);
@@ -127,6 +127,7 @@ struct WindowAttnParams {
   int gate_per_head;        // 1: gate is [B, T, Hq], one sigmoid factor per head instead of one per output channel
   int chunk;                // > 0: key j is visible from position p only when j / chunk == p / chunk (instead of a window)
   const float* slopes;      // [Hq] or null: slopes[h] * (p - j) is taken off the score of head h
+  const float* head_scale;  // [Hq] or null: the score of head h is multiplied by head_scale[h] as well (a learned temperature per head)
   long long v_rs;           // elements between the value rows of neighbouring (token, kv head) pairs; Dv <= v_rs (values that are a
                             // prefix of a wider cache row: v_cache = k_cache, v_rs = D)
 };
@@ -143,6 +144,59 @@ struct SsdScanParams {
   int B, T, nh, P, N, G;
 };
 void ssd_scan_launch(const SsdScanParams& p, bool lp, cudaStream_t st);
+
+// Update of an fp32 residual stream whose sublayers are normalised on both sides, and the norm the next sublayer reads:
+//   y = a_scale * f_a(a) + b_scale * f_b(b), f(v) = rms_unit(v) * weight when the weight is given, else v   (b optional)
+//   s = x + mult * ls * norm(y) * post_w   (s = x when a is null);   h = norm(s) * next_w   (when next_w is given)
+// norm: layer norm without bias when center, RMS norm otherwise.  All arithmetic fp32; a / b share one activation type.
+struct SandwichParams {
+  const float* x;                  // [rows, W]
+  const void *a, *b;               // [rows, W] or null
+  const float *a_w, *b_w;          // [W] or null
+  const float *post_w, *ls;        // [W] or null
+  const float* next_w;             // [W] or null
+  float* s;                        // [rows, W]
+  void* h;                         // [rows, W] bf16 or fp32, or null
+  int rows, W, center;
+  float a_scale, b_scale, mult, eps;
+};
+void stream_sandwich_norm_launch(const SandwichParams& p, bool y_lp, bool h_lp, cudaStream_t st);
+
+// Per-head RMS norm (before or after the rotation, weights [D] shared by the heads or null) + rotate-half rotation of the first R
+// channels of every q / k head + paged cache write.  value_from_key: the raw k slice doubles as the value (no v slice, Dv == D).
+struct HeadNormRopeParams {
+  const void* p;            // [B, T, >= Cq + Ck (+ Cv)] projections q | k | v, row strides below
+  long long p_sb, p_st;
+  const float *q_w, *k_w;   // [D] or null
+  const float *cos, *sin;   // [B, T, R / 2] or null
+  void* q_out;              // [B, T, n_q, D]
+  void *k_cache, *v_cache;  // [blocks, page, n_kv, D | Dv]
+  const int *block_table, *ctx_len, *q_len;
+  int B, T, n_q, n_kv, D, Dv, R, page, max_blocks;
+  int norm_at;              // 0 none, 1 before the rotation, 2 after it
+  int value_from_key;
+  float eps;
+};
+void head_norm_rope_append_launch(const HeadNormRopeParams& p, bool lp, cudaStream_t st);
+
+// Gated delta rule with a carried fp32 state M [lines, nh, D, Dv]: q / k scaled to unit length (q also by D^-1/2), b = sigmoid(beta_raw),
+// log decay = -exp(A_log) * softplus(a_raw + dt_bias); per step M *= decay, e = b * (v - M' k), M += outer(k, e), y = M' q.
+struct DeltaScanParams {
+  const float* qkv;         // [B, T, 2 n_qk D + nh Dv] after convolution and activation
+  const void *beta_raw, *a_raw;      // [B, T, nh] strided views of the in-projection, activation type
+  long long beta_sb, beta_st, a_sb, a_st;
+  const float *A_log, *dt_bias;
+  float* state;             // [lines, nh, D, Dv]
+  const int *lines, *ctx_len, *q_len;
+  float* o;                 // [B, T, nh * Dv]
+  int B, T, nh, n_qk, D, Dv;
+  float unit_eps;
+};
+void gated_delta_scan_launch(const DeltaScanParams& p, bool lp, cudaStream_t st);
+
+// out[row, h, :] = rms_unit(y[row, h, :]) * w[:] * act(gate[row, h, :]); w [Dv] is shared by the heads; gate rows g_stride elements apart
+void head_rmsnorm_gate_launch(const float* y, const float* w, const void* gate, long long g_stride, void* out, long long rows, int H, int Dv,
+                              float eps, int act, bool gate_lp, bool out_lp, cudaStream_t st);
 
 void group_rmsnorm_launch(const float* y, const float* w, void* out, bool out_lp, int rows, int W, int groups, float eps, cudaStream_t st);
 

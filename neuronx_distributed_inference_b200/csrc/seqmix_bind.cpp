@@ -154,7 +154,7 @@ at::Tensor conv_qknorm_rope_append(const at::Tensor& p, const at::Tensor& conv_w
 at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache, const at::Tensor& block_table,
                                   const at::Tensor& ctx, const at::Tensor& qlen, double scale, double softcap, int64_t window,
                                   int64_t keep_first, const OptT& gate, const OptT& sinks, bool gate_per_head, int64_t chunk, const OptT& slopes,
-                                  int64_t value_dim) {
+                                  int64_t value_dim, const OptT& head_scale) {
   check_act(q, "paged_window_attention q");
   TORCH_CHECK(q.dim() == 4 && q.is_contiguous());
   const int64_t B = q.size(0), T = q.size(1), Hq = q.size(2), D = q.size(3);
@@ -186,6 +186,11 @@ at::Tensor paged_window_attention(const at::Tensor& q, const at::Tensor& k_cache
     check_f32(*slopes, "slopes");
     TORCH_CHECK(slopes->numel() == Hq, "slopes: one per query head");
     a.slopes = slopes->data_ptr<float>();
+  }
+  if (head_scale.has_value()) {
+    check_f32(*head_scale, "head_scale");
+    TORCH_CHECK(head_scale->numel() == Hq, "head_scale: one per query head");
+    a.head_scale = head_scale->data_ptr<float>();
   }
   a.chunk = (int)chunk;
   a.v_rs = v_cache.size(3);
@@ -517,7 +522,138 @@ void identity_expert_add(at::Tensor y, const at::Tensor& x, const at::Tensor& to
 
 }  // namespace
 
+
+inline const float* opt_f32(const OptT& t, int64_t n, const char* what) {
+  if (!t.has_value()) return nullptr;
+  check_f32(*t, what);
+  TORCH_CHECK(t->numel() == n, what, ": ", n, " numbers");
+  return t->data_ptr<float>();
+}
+
+std::tuple<at::Tensor, OptT> stream_sandwich_norm(const at::Tensor& x, const OptT& a, const OptT& b, const OptT& a_w, const OptT& b_w, double a_scale,
+                                                  double b_scale, const OptT& post_w, const OptT& ls, double mult, const OptT& next_w, double eps,
+                                                  bool center, bool h_lp) {
+  check_f32(x, "stream_sandwich_norm x");
+  TORCH_CHECK(x.dim() == 2);
+  const int64_t rows = x.size(0), W = x.size(1);
+  TORCH_CHECK(W * 4 <= 200 * 1024, "stream_sandwich_norm: rows of at most 51200 numbers");
+  TORCH_CHECK(a.has_value() || !b.has_value(), "stream_sandwich_norm: b without a");
+  bool y_lp = false;
+  for (const OptT* t : {&a, &b}) {
+    if (!t->has_value()) continue;
+    check_act(**t, "stream_sandwich_norm a / b");
+    TORCH_CHECK((*t)->is_contiguous() && (*t)->sizes() == x.sizes(), "stream_sandwich_norm: a / b like x, contiguous");
+    y_lp = is_lp(**t);
+  }
+  TORCH_CHECK(!(a.has_value() && b.has_value()) || a->scalar_type() == b->scalar_type(), "stream_sandwich_norm: a and b of one type");
+  SandwichParams p{};
+  p.x = x.data_ptr<float>();
+  p.a = a.has_value() ? a->data_ptr() : nullptr;
+  p.b = b.has_value() ? b->data_ptr() : nullptr;
+  p.a_w = opt_f32(a_w, W, "a weight"); p.b_w = opt_f32(b_w, W, "b weight");
+  p.post_w = opt_f32(post_w, W, "post weight"); p.ls = opt_f32(ls, W, "layer scale"); p.next_w = opt_f32(next_w, W, "next weight");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto s = at::empty_like(x);
+  OptT h;
+  if (next_w.has_value()) h = at::empty(x.sizes(), x.options().dtype(h_lp ? at::kBFloat16 : at::kFloat));
+  p.s = s.data_ptr<float>();
+  p.h = h.has_value() ? h->data_ptr() : nullptr;
+  p.rows = (int)rows; p.W = (int)W; p.center = center ? 1 : 0;
+  p.a_scale = (float)a_scale; p.b_scale = (float)b_scale; p.mult = (float)mult; p.eps = (float)eps;
+  stream_sandwich_norm_launch(p, y_lp, h_lp, stream());
+  return {s, h};
+}
+
+at::Tensor head_norm_rope_append(const at::Tensor& pr, int64_t n_q, int64_t n_kv, int64_t D, int64_t Dv, const OptT& cos, const OptT& sin,
+                                 const OptT& q_w, const OptT& k_w, int64_t norm_at, double eps, bool value_from_key, at::Tensor k_cache,
+                                 at::Tensor v_cache, const at::Tensor& block_table, const at::Tensor& ctx, const at::Tensor& qlen) {
+  check_act(pr, "head_norm_rope_append rows");
+  check_rows(pr, "head_norm_rope_append rows");
+  const int64_t B = pr.size(0), T = pr.size(1);
+  const int64_t need = n_q * D + n_kv * D + (value_from_key ? 0 : n_kv * Dv);
+  TORCH_CHECK(pr.size(2) >= need && D >= 1 && D <= 256 && Dv >= 1 && (!value_from_key || Dv == D), "head_norm_rope_append: q | k | v slices, head size <= 256");
+  TORCH_CHECK(norm_at >= 0 && norm_at <= 2);
+  TORCH_CHECK(k_cache.is_cuda() && k_cache.scalar_type() == pr.scalar_type() && k_cache.is_contiguous() && k_cache.dim() == 4 &&
+              k_cache.size(2) == n_kv && k_cache.size(3) == D, "head_norm_rope_append: key cache [blocks, page, kv heads, D]");
+  TORCH_CHECK(v_cache.is_cuda() && v_cache.scalar_type() == pr.scalar_type() && v_cache.is_contiguous() && v_cache.dim() == 4 &&
+              v_cache.size(0) == k_cache.size(0) && v_cache.size(1) == k_cache.size(1) && v_cache.size(2) == n_kv && v_cache.size(3) == Dv,
+              "head_norm_rope_append: value cache [blocks, page, kv heads, Dv]");
+  TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == at::kInt && block_table.is_contiguous() && block_table.dim() == 2 &&
+              block_table.size(0) == B);
+  check_i32(ctx, B, "ctx_len");
+  check_i32(qlen, B, "q_len");
+  HeadNormRopeParams p{};
+  if (cos.has_value()) {
+    TORCH_CHECK(sin.has_value());
+    check_f32(*cos, "cos"); check_f32(*sin, "sin");
+    TORCH_CHECK(cos->dim() == 3 && cos->size(0) == B && cos->size(1) == T && cos->sizes() == sin->sizes() && 2 * cos->size(2) <= D,
+                "cos / sin: [B, T, R / 2] with R <= D");
+    p.cos = cos->data_ptr<float>(); p.sin = sin->data_ptr<float>(); p.R = (int)(2 * cos->size(2));
+  }
+  p.q_w = opt_f32(q_w, D, "q norm weight"); p.k_w = opt_f32(k_w, D, "k norm weight");
+  c10::cuda::CUDAGuard guard(pr.device());
+  auto q = at::zeros({B, T, n_q, D}, pr.options());
+  p.p = pr.data_ptr(); p.p_sb = pr.stride(0); p.p_st = pr.stride(1);
+  p.q_out = q.data_ptr(); p.k_cache = k_cache.data_ptr(); p.v_cache = v_cache.data_ptr();
+  p.block_table = block_table.data_ptr<int>(); p.ctx_len = ctx.data_ptr<int>(); p.q_len = qlen.data_ptr<int>();
+  p.B = (int)B; p.T = (int)T; p.n_q = (int)n_q; p.n_kv = (int)n_kv; p.D = (int)D; p.Dv = (int)Dv; p.page = (int)k_cache.size(1);
+  p.max_blocks = (int)block_table.size(1); p.norm_at = (int)norm_at; p.value_from_key = value_from_key ? 1 : 0; p.eps = (float)eps;
+  head_norm_rope_append_launch(p, is_lp(pr), stream());
+  return q;
+}
+
+at::Tensor gated_delta_scan(const at::Tensor& qkv, const at::Tensor& beta_raw, const at::Tensor& a_raw, const at::Tensor& A_log,
+                            const at::Tensor& dt_bias, at::Tensor state, const at::Tensor& lines, const at::Tensor& ctx, const at::Tensor& qlen,
+                            int64_t nh, int64_t n_qk, int64_t D, int64_t Dv, double unit_eps) {
+  check_f32(qkv, "gated_delta_scan q | k | v");
+  TORCH_CHECK(qkv.dim() == 3 && qkv.size(2) == 2 * n_qk * D + nh * Dv && nh % n_qk == 0 && D >= 1 && D <= 256, "gated_delta_scan: sizes (D <= 256)");
+  const int64_t B = qkv.size(0), T = qkv.size(1);
+  for (const at::Tensor* t : {&beta_raw, &a_raw}) {
+    check_act(*t, "gated_delta_scan beta / a");
+    check_rows(*t, "gated_delta_scan beta / a");
+    TORCH_CHECK(t->size(0) == B && t->size(1) == T && t->size(2) == nh);
+  }
+  TORCH_CHECK(beta_raw.scalar_type() == a_raw.scalar_type());
+  check_f32(A_log, "A_log"); check_f32(dt_bias, "dt_bias");
+  TORCH_CHECK(A_log.numel() == nh && dt_bias.numel() == nh);
+  check_f32(state, "gated_delta_scan state");
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == nh && state.size(2) == D && state.size(3) == Dv, "gated_delta_scan: state [lines, heads, D, Dv]");
+  check_i32(lines, B, "lines"); check_i32(ctx, B, "ctx_len"); check_i32(qlen, B, "q_len");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  auto o = at::zeros({B, T, nh * Dv}, qkv.options());
+  DeltaScanParams p{};
+  p.qkv = qkv.data_ptr<float>();
+  p.beta_raw = beta_raw.data_ptr(); p.beta_sb = beta_raw.stride(0); p.beta_st = beta_raw.stride(1);
+  p.a_raw = a_raw.data_ptr(); p.a_sb = a_raw.stride(0); p.a_st = a_raw.stride(1);
+  p.A_log = A_log.data_ptr<float>(); p.dt_bias = dt_bias.data_ptr<float>(); p.state = state.data_ptr<float>();
+  p.lines = lines.data_ptr<int>(); p.ctx_len = ctx.data_ptr<int>(); p.q_len = qlen.data_ptr<int>();
+  p.o = o.data_ptr<float>();
+  p.B = (int)B; p.T = (int)T; p.nh = (int)nh; p.n_qk = (int)n_qk; p.D = (int)D; p.Dv = (int)Dv; p.unit_eps = (float)unit_eps;
+  gated_delta_scan_launch(p, is_lp(beta_raw), stream());
+  return o;
+}
+
+at::Tensor head_rmsnorm_gate(const at::Tensor& y, const at::Tensor& w, int64_t heads, double eps, const at::Tensor& gate, int64_t act, bool out_lp) {
+  check_f32(y, "head_rmsnorm_gate y");
+  check_f32(w, "head_rmsnorm_gate weight");
+  TORCH_CHECK(y.dim() == 2 && y.size(1) % heads == 0);
+  const int64_t rows = y.size(0), Dv = y.size(1) / heads;
+  TORCH_CHECK(w.numel() == Dv && Dv <= SEQMIX_MAX_VDIM, "head_rmsnorm_gate: weight [Dv], Dv <= ", SEQMIX_MAX_VDIM);
+  check_act(gate, "head_rmsnorm_gate gate");
+  TORCH_CHECK(gate.dim() == 2 && gate.size(0) == rows && gate.size(1) == y.size(1) && gate.stride(1) == 1, "head_rmsnorm_gate: gate [rows, heads * Dv]");
+  c10::cuda::CUDAGuard guard(y.device());
+  auto out = at::empty(y.sizes(), y.options().dtype(out_lp ? at::kBFloat16 : at::kFloat));
+  head_rmsnorm_gate_launch(y.data_ptr<float>(), w.data_ptr<float>(), gate.data_ptr(), gate.stride(0), out.data_ptr(), rows, (int)heads, (int)Dv,
+                           (float)eps, (int)act, is_lp(gate), out_lp, stream());
+  return out;
+}
+
+
 void register_seqmix(pybind11::module_& m) {
+  m.def("stream_sandwich_norm", &stream_sandwich_norm);
+  m.def("head_norm_rope_append", &head_norm_rope_append);
+  m.def("gated_delta_scan", &gated_delta_scan);
+  m.def("head_rmsnorm_gate", &head_rmsnorm_gate);
   m.def("router_topk", &router_topk);
   m.def("rope_half_tail", &rope_half_tail);
   m.def("stream_norm_conv", &stream_norm_conv);

@@ -442,7 +442,7 @@ def moe_experts(x, w_gate_up, w_down, topk_w, topk_i, act="silu_mul", expert_off
 
 _MOE_GROUPED = os.environ.get("NXDI_B200_MOE_GROUPED", "1") == "1"
 _MOE_ACTS = {"silu_mul": 1, "gelu_tanh_mul": 2, "gelu_mul": 3, "gpt_oss_glu": 4}
-_UNARY_ACTS = {"relu": 1, "relu2": 2, "silu": 3, "gelu_tanh": 4, "sigmoid": 5}         # codes of csrc/seqmix.cu (unary_act, moe_plain, gated_act_mul)
+_UNARY_ACTS = {"relu": 1, "relu2": 2, "silu": 3, "gelu_tanh": 4, "sigmoid": 5, "gelu": 6}         # codes of csrc/seqmix.cu (unary_act, moe_plain, gated_act_mul)
 _MOE_PLAIN_ACTS = _UNARY_ACTS
 
 
@@ -526,16 +526,17 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
 
 
 def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate=None, sinks=None,
-                           gate_per_head: bool = False, chunk=None, slopes=None, value_dim=None):
+                           gate_per_head: bool = False, chunk=None, slopes=None, value_dim=None, head_scale=None):
     Dv = v_cache.shape[-1] if value_dim is None else int(value_dim)
     if _mix_cuda(q) and k_cache.dtype == q.dtype and (gate is None or gate.stride(-1) == 1) and Dv <= _MIX_MAX_VDIM and not (chunk and window):
         stats["paged_window_attention"] += 1
         return _C().paged_window_attention(q.contiguous(), k_cache, v_cache, _i32(block_table), _i32(ctx_len), _i32(q_len), float(scale),
                                            float(softcap or 0.0), int(window or 0), int(keep_first or 0), gate,
                                            None if sinks is None else sinks.float().contiguous(), bool(gate_per_head), int(chunk or 0),
-                                           None if slopes is None else slopes.float().contiguous(), Dv)
+                                           None if slopes is None else slopes.float().contiguous(), Dv,
+                                           None if head_scale is None else head_scale.float().contiguous())
     return ref.paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale, softcap, window, keep_first, gate, sinks,
-                                      gate_per_head, chunk, slopes, value_dim)
+                                      gate_per_head, chunk, slopes, value_dim, head_scale)
 
 
 def ssd_scan(xBC, dt_raw, z, A_log, dt_bias, D_skip, state, slots, ctx_len, q_len, n_heads, head_dim, n_state, n_groups):
@@ -660,3 +661,56 @@ def unary_act(x, act: str):
         stats["unary_act"] += 1
         return _C().unary_act(x.reshape(-1, x.shape[-1]), _UNARY_ACTS[act]).view(x.shape)
     return ref.unary_act(x, act)
+
+
+def stream_sandwich_norm(x, a=None, b=None, a_weight=None, b_weight=None, a_scale: float = 1.0, b_scale: float = 1.0, post_weight=None,
+                         layer_scale=None, mult: float = 1.0, next_weight=None, eps: float = 1e-6, center: bool = True, lp_dtype=None):
+    """Stream update of a block normalised on both sides of its sublayers + the norm the next sublayer reads, ONE kernel (definition:
+    ops/reference.py)."""
+    ys = tuple(t for t in (a, b) if t is not None)
+    if (_use_cuda(x) and x.dtype == torch.float32 and all(t.dtype in _MIX_DTYPES for t in ys) and len({t.dtype for t in ys}) <= 1
+            and x.shape[-1] <= 51200 and not (a is None and b is not None)):
+        stats["stream_sandwich_norm"] += 1
+        W = x.shape[-1]
+        flat = lambda t: None if t is None else t.reshape(-1, W).contiguous()          # noqa: E731
+        f32 = lambda t: None if t is None else t.float().contiguous()                  # noqa: E731
+        s, h = _C().stream_sandwich_norm(flat(x), flat(a), flat(b), f32(a_weight), f32(b_weight), float(a_scale), float(b_scale),
+                                         f32(post_weight), f32(layer_scale), float(mult), f32(next_weight), float(eps), bool(center),
+                                         lp_dtype == torch.bfloat16)
+        return s.view(x.shape), (None if h is None else h.view(x.shape))
+    return ref.stream_sandwich_norm(x, a, b, a_weight, b_weight, a_scale, b_scale, post_weight, layer_scale, mult, next_weight, eps, center,
+                                    lp_dtype)
+
+
+def head_norm_rope_append(p, n_q, n_kv, D, Dv, cos, sin, q_norm_w, k_norm_w, norm_at: int, eps: float, value_from_key: bool, k_cache, v_cache,
+                          block_table, ctx_len, q_len, out_dtype=None):
+    """Per-head q / k RMS norm (before or after the rotation) + rotate-half rotation + paged cache write, ONE kernel (definition:
+    ops/reference.py)."""
+    if _mix_cuda(p) and p.stride(-1) == 1 and D <= 256 and k_cache.dtype == p.dtype and v_cache.dtype == p.dtype and (cos is None or cos.shape[-1] * 2 <= D):
+        stats["head_norm_rope_append"] += 1
+        f32 = lambda t: None if t is None else t.float().contiguous()          # noqa: E731
+        return _C().head_norm_rope_append(p, int(n_q), int(n_kv), int(D), int(Dv), f32(cos), f32(sin), f32(q_norm_w), f32(k_norm_w), int(norm_at),
+                                          float(eps), bool(value_from_key), k_cache, v_cache, _i32(block_table), _i32(ctx_len), _i32(q_len))
+    return ref.head_norm_rope_append(p, n_q, n_kv, D, Dv, cos, sin, q_norm_w, k_norm_w, norm_at, eps, value_from_key, k_cache, v_cache,
+                                     block_table, ctx_len, q_len, out_dtype)
+
+
+def gated_delta_scan(qkv, beta_raw, a_raw, A_log, dt_bias, state, slots, ctx_len, q_len, n_heads, n_qk, D, Dv, unit_eps: float = 1e-6):
+    if (_use_cuda(qkv) and qkv.dtype == torch.float32 and beta_raw.dtype in _MIX_DTYPES and a_raw.dtype == beta_raw.dtype
+            and state.dtype == torch.float32 and D <= 256 and beta_raw.stride(-1) == 1 and a_raw.stride(-1) == 1):
+        stats["gated_delta_scan"] += 1
+        return _C().gated_delta_scan(qkv.contiguous(), beta_raw, a_raw, A_log, dt_bias, state, _i32(slots), _i32(ctx_len), _i32(q_len),
+                                     int(n_heads), int(n_qk), int(D), int(Dv), float(unit_eps))
+    return ref.gated_delta_scan(qkv, beta_raw, a_raw, A_log, dt_bias, state, slots, ctx_len, q_len, n_heads, n_qk, D, Dv, unit_eps)
+
+
+def head_rmsnorm_gate(y, weight, heads: int, eps: float, gate, act: str = "silu", out_dtype=None):
+    od = out_dtype or y.dtype
+    C = y.shape[-1]
+    if (_use_cuda(y) and y.dtype == torch.float32 and od in _MIX_DTYPES and gate.dtype in _MIX_DTYPES and gate.stride(-1) == 1 and act in _UNARY_ACTS
+            and C // heads <= _MIX_MAX_VDIM and gate.shape == y.shape):
+        stats["head_rmsnorm_gate"] += 1
+        g2 = gate if gate.dim() == 2 else (gate.reshape(-1, C) if gate.is_contiguous() else _rows_view(gate))
+        return _C().head_rmsnorm_gate(y.reshape(-1, C).contiguous(), weight.float().contiguous(), int(heads), float(eps), g2, _UNARY_ACTS[act],
+                                      od == torch.bfloat16).view(y.shape)
+    return ref.head_rmsnorm_gate(y, weight, heads, eps, gate, act, out_dtype)

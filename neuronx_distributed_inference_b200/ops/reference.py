@@ -484,7 +484,7 @@ def conv_qknorm_rope_append(qkv, conv_w, state, slots, ctx_len, q_len, q_norm_w,
 
 
 def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, scale: float, softcap: float, window: int,
-                           keep_first: int, gate=None, sinks=None, gate_per_head: bool = False, chunk=None, slopes=None, value_dim=None):
+                           keep_first: int, gate=None, sinks=None, gate_per_head: bool = False, chunk=None, slopes=None, value_dim=None, head_scale=None):
     """Soft-capped attention of ragged query rows over a paged cache that already holds their own keys.  Query at position
     ``p = ctx_len + t`` sees key ``j`` iff ``j <= p and (p - j < window or j < keep_first)``; ``window <= 0`` means unbounded.
     score = cap * tanh(scale * q.k / cap) (cap <= 0: none), softmax in fp32.  ``gate`` [B, T, Hq * Dv]: the output is multiplied by
@@ -493,6 +493,7 @@ def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, sca
     from positions of its own chunk, ``j // chunk == p // chunk`` (chunks count from position 0 of the sequence).  ``slopes`` [Hq] fp32:
     ``slopes[h] * (p - j)`` is taken off the score of head ``h`` (after scale and cap).  ``value_dim``: the value of a key is the first
     ``value_dim`` channels of the row in ``v_cache`` (latent caches whose key row is the latent followed by a rotated part).
+    ``head_scale`` [Hq] fp32: the score of head ``h`` is multiplied by ``head_scale[h]`` as well (a learned temperature per head).
     q [B, T, Hq, D] -> [B, T, Hq * Dv]."""
     B, T, Hq, D = q.shape
     if value_dim is not None:
@@ -511,6 +512,8 @@ def paged_window_attention(q, k_cache, v_cache, block_table, ctx_len, q_len, sca
         see = see & (torch.div(j, chunk, rounding_mode="floor") == torch.div(p, chunk, rounding_mode="floor"))
     rep = Hq // G
     s = torch.einsum("bthd,bshd->bhts", q.float(), k.repeat_interleave(rep, 2)) * scale
+    if head_scale is not None:
+        s = s * head_scale.float().view(1, Hq, 1, 1)
     if softcap and softcap > 0:
         s = softcap * torch.tanh(s / softcap)
     if slopes is not None:
@@ -680,3 +683,122 @@ def gated_act_mul(gate, other, act: str = "gelu_tanh", act_on_other: bool = Fals
 
 def unary_act(x, act: str):
     return activation(x.float(), act).to(x.dtype)
+
+
+# ---- sandwich-norm blocks, per-head norms around a rotate-half rotation, the gated delta rule -------------------------------------
+def _norm_rows(v, center: bool, eps: float):
+    """``v`` over its last axis: minus its mean when ``center``, divided by the root of the mean square (of the deviations) + eps."""
+    if center:
+        v = v - v.mean(-1, keepdim=True)
+    return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def stream_sandwich_norm(x, a=None, b=None, a_weight=None, b_weight=None, a_scale: float = 1.0, b_scale: float = 1.0, post_weight=None,
+                         layer_scale=None, mult: float = 1.0, next_weight=None, eps: float = 1e-6, center: bool = True, lp_dtype=None):
+    """One update of an fp32 residual stream whose sublayers are normalised on BOTH sides, plus the norm the next sublayer reads::
+
+        y = a_scale * f_a(a) + b_scale * f_b(b)        f(v) = rms_unit(v) * weight when a weight is given, else v   (b optional)
+        s = x + mult * layer_scale * norm(y) * post_weight                                        (s = x when a is None)
+        h = norm(s) * next_weight                                                                 (when next_weight is given)
+
+    ``norm`` is a layer norm without bias when ``center`` (mean taken off, variance of the deviations), an RMS norm otherwise; all of it
+    is fp32, nothing between ``a`` / ``b`` and ``s`` is rounded.  Returns ``(s fp32, h in lp_dtype or None)``."""
+    s = x.float()
+    if a is not None:
+        def side(v, w, sc):
+            v = v.float()
+            if w is not None:
+                v = _norm_rows(v, False, eps) * w.float()
+            return v * sc
+        y = side(a, a_weight, a_scale)
+        if b is not None:
+            y = y + side(b, b_weight, b_scale)
+        y = _norm_rows(y, center, eps)
+        if post_weight is not None:
+            y = y * post_weight.float()
+        if layer_scale is not None:
+            y = y * layer_scale.float()
+        s = s + mult * y
+    h = None
+    if next_weight is not None:
+        h = _norm_rows(s, center, eps) * next_weight.float()
+        h = h if lp_dtype in (None, torch.float32) else h.to(lp_dtype)
+    return s, h
+
+
+def head_norm_rope_append(p, n_q: int, n_kv: int, D: int, Dv: int, cos, sin, q_norm_w, k_norm_w, norm_at: int, eps: float,
+                          value_from_key: bool, k_cache, v_cache, block_table, ctx_len, q_len, out_dtype=None):
+    """Front half of a grouped-query attention layer on ragged rows.  ``p`` [B, T, >= n_q D + n_kv D (+ n_kv Dv)] holds q | k | v
+    (no v slice when ``value_from_key``: the raw k slice doubles as the value, untouched by norm or rotation, so ``Dv == D``).
+    Every q and k head is RMS-normalised over its ``D`` channels (``norm_at`` 1: before the rotation, 2: after it, 0: not at all;
+    ``q_norm_w`` / ``k_norm_w`` [D] are shared by the heads, ``None`` = no weight) and its first ``2 * cos.shape[-1]`` channels are
+    rotated in the rotate-half layout (channel ``i`` pairs with ``i + R / 2``); ``cos = None`` skips the rotation.  Keys and values go
+    to the paged caches ``[blocks, page, n_kv, D | Dv]`` at position ``ctx_len + t``.  Returns q [B, T, n_q, D]."""
+    B, T = p.shape[:2]
+    Cq, Ck = n_q * D, n_kv * D
+    q = p[..., :Cq].float().reshape(B, T, n_q, D)
+    k_raw = p[..., Cq:Cq + Ck].float().reshape(B, T, n_kv, D)
+    v = k_raw if value_from_key else p[..., Cq + Ck:Cq + Ck + n_kv * Dv].float().reshape(B, T, n_kv, Dv)
+
+    def prep(x, w):
+        if norm_at == 1:
+            x = _norm_rows(x, False, eps)
+            if w is not None:
+                x = x * w.float()
+        if cos is not None:
+            R = 2 * cos.shape[-1]
+            x = torch.cat([rotate_half_rows(x[..., :R], cos.float().unsqueeze(2), sin.float().unsqueeze(2)), x[..., R:]], -1)
+        if norm_at == 2:
+            x = _norm_rows(x, False, eps)
+            if w is not None:
+                x = x * w.float()
+        return x
+    q, k = prep(q, q_norm_w), prep(k_raw, k_norm_w)
+    page = k_cache.shape[1]
+    t = torch.arange(T, device=p.device).view(1, T)
+    pos = ctx_len.long().view(B, 1) + t
+    ok = t < q_len.long().view(B, 1)
+    blk = torch.gather(block_table.long(), 1, (pos // page).clamp(0, block_table.shape[1] - 1))
+    slot = (blk * page + pos % page)[ok]
+    k_cache.view(-1, n_kv, D)[slot] = k[ok].to(k_cache.dtype)
+    v_cache.view(-1, n_kv, Dv)[slot] = v[ok].to(v_cache.dtype)
+    return q.to(out_dtype or p.dtype)
+
+
+def gated_delta_scan(qkv, beta_raw, a_raw, A_log, dt_bias, state, slots, ctx_len, q_len, n_heads: int, n_qk: int, D: int, Dv: int,
+                     unit_eps: float = 1e-6):
+    """Gated delta rule with a carried fp32 state ``[lines, n_heads, D, Dv]``.  ``qkv`` [B, T, 2 n_qk D + n_heads Dv] is q | k | v after
+    their convolutions and activations; head ``h`` reads q / k head ``h // (n_heads / n_qk)``.  q and k are scaled to unit length
+    (``unit_eps`` under the root) and q also by ``D^-1/2``; write strength ``b = sigmoid(beta_raw)``, decay with
+    ``log decay = -exp(A_log) * softplus(a_raw + dt_bias)`` (both [B, T, n_heads]).  Per head and step the state ``M`` is shrunk,
+    ``M *= decay``, corrected along k towards v, ``e = b * (v - M' k)``, ``M += outer(k, e)``, and read AFTER the correction,
+    ``y = M' q``.  Returns y fp32 [B, T, n_heads * Dv]; padding steps leave the state untouched."""
+    B, T = qkv.shape[:2]
+    H, rep = n_heads, n_heads // n_qk
+    Cq = n_qk * D
+    unit = lambda x: x * torch.rsqrt(x.pow(2).sum(-1, keepdim=True) + unit_eps)          # noqa: E731
+    q = (unit(qkv[..., :Cq].float().reshape(B, T, n_qk, D)) * D ** -0.5).repeat_interleave(rep, 2)
+    k = unit(qkv[..., Cq:2 * Cq].float().reshape(B, T, n_qk, D)).repeat_interleave(rep, 2)
+    v = qkv[..., 2 * Cq:2 * Cq + H * Dv].float().reshape(B, T, H, Dv)
+    beta = torch.sigmoid(beta_raw.float())
+    g = torch.exp(-torch.exp(A_log.float()) * F.softplus(a_raw.float() + dt_bias.float(), threshold=1e9))
+    S = state[slots.long()].float()
+    S = torch.where((ctx_len > 0).view(B, 1, 1, 1), S, torch.zeros_like(S))
+    out = []
+    for t in range(T):
+        live = (t < q_len).view(B, 1, 1, 1)
+        Sd = S * g[:, t, :, None, None]
+        u = beta[:, t, :, None] * (v[:, t] - torch.einsum("bhdv,bhd->bhv", Sd, k[:, t]))
+        Sn = Sd + k[:, t, :, :, None] * u[:, :, None, :]
+        S = torch.where(live, Sn, S)
+        out.append(torch.einsum("bhdv,bhd->bhv", S, q[:, t]))
+    state[slots.long()] = torch.where((q_len > 0).view(B, 1, 1, 1), S, state[slots.long()].float()).to(state.dtype)
+    return torch.stack(out, 1).reshape(B, T, H * Dv)
+
+
+def head_rmsnorm_gate(y, weight, heads: int, eps: float, gate, act: str = "silu", out_dtype=None):
+    """``y`` [..., heads * Dv] fp32: every head is divided by its root mean square over ``Dv``, times ``weight`` [Dv] (shared by the
+    heads), times ``act(gate)`` (``gate`` [..., heads * Dv], possibly a strided slice of a wider row); the gate comes AFTER the norm."""
+    Dv = y.shape[-1] // heads
+    yf = _norm_rows(y.float().reshape(*y.shape[:-1], heads, Dv), False, eps) * weight.float()
+    return (yf.reshape(y.shape) * activation(gate.float(), act)).to(out_dtype or y.dtype)
