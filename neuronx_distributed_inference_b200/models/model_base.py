@@ -182,6 +182,51 @@ class ConvPreNormDecoderLayer(nn.Module):
         return x, y
 
 
+class SandwichNormDecoderLayer(nn.Module):
+    """Block on an fp32 residual stream whose sublayers are normalised on BOTH sides, with a residual multiplier and a layer scale:
+    ``r = mixer(norm1(x))``, ``x += mult * ls1 * norm1b(r)``, then, when the block has an MLP, ``r = mlp(norm2(x))``, ``x += mult * ls2 * norm2b(r)``.
+    The norms are layer norms with a weight and no bias (``center=True``) or RMS norms (``center=False``); ``ls*`` are learned vectors
+    over the width.  A mixer may return a :class:`MixerPair` (two results and how they combine); the combination, the post-norm, the
+    layer scale, the sum and the NEXT sublayer's pre-norm are ONE fp32 kernel (``ops.stream_sandwich_norm``), so the output of a block's
+    last sublayer is handed on unadded: ``forward`` takes and returns ``(x, pending)``, ``pending`` being the keyword arguments of that
+    kernel (``SandwichNormDecoderLayer.finish`` applies them after the last block)."""
+    mlp_is_moe = False
+
+    def __init__(self, mixer: nn.Module, mlp: Optional[nn.Module], norm1: nn.Module, norm1b: nn.Module, norm2: Optional[nn.Module],
+                 norm2b: Optional[nn.Module], width: int, mult: float, center: bool = True, layer_idx: int = 0, device=None):
+        super().__init__()
+        self.mixer, self.mlp, self.norm1, self.norm1b, self.norm2, self.norm2b = mixer, mlp, norm1, norm1b, norm2, norm2b
+        self.mult, self.center, self.layer_idx = float(mult), bool(center), layer_idx
+        ls = lambda: nn.Parameter(torch.ones(width, dtype=torch.float32, device=device), requires_grad=False)      # noqa: E731
+        self.ls1 = ls()
+        self.ls2 = ls() if mlp is not None else None
+
+    def state_specs(self, run=None):
+        return getattr(self.mixer, "state_specs", dict)(run)
+
+    def _pending(self, y, post, ls):
+        pair = y if isinstance(y, tuple) else (y, None, None, None, 1.0, 1.0)
+        a, b, aw, bw, sa, sb = pair
+        return dict(a=a, b=b, a_weight=aw, b_weight=bw, a_scale=sa, b_scale=sb, post_weight=post.weight, layer_scale=ls, mult=self.mult,
+                    eps=post.eps, center=self.center)
+
+    @staticmethod
+    def finish(x, pending, next_weight=None, eps=1e-6, center=True, lp_dtype=None):
+        """Apply a handed-on sublayer output to the stream (and form the norm ``next_weight`` asks for)."""
+        kw = dict(pending) if pending else dict(eps=eps, center=center)
+        return ops.stream_sandwich_norm(x, next_weight=next_weight, lp_dtype=lp_dtype, **kw)
+
+    def forward(self, x, pending, meta, kv_mgr, cache_index=None):
+        dtype = meta.extras["act_dtype"]
+        x, h = self.finish(x, pending, self.norm1.weight, self.norm1.eps, self.center, dtype)
+        y = self.mixer(h, meta, kv_mgr, cache_index=cache_index)
+        pending = self._pending(y, self.norm1b, self.ls1)
+        if self.mlp is not None:
+            x, h = self.finish(x, pending, self.norm2.weight, self.norm2.eps, self.center, dtype)
+            pending = self._pending(self.mlp(h), self.norm2b, self.ls2)
+        return x, pending
+
+
 class NeuronBaseModel(nn.Module):
     """Generic causal decoder.  Subclass hooks: ``setup_attr_for_model(config)`` (set
     ``tp_degree, hidden_size, num_attention_heads, num_key_value_heads, max_batch_size,

@@ -101,7 +101,8 @@ MODEL_TYPES["fetodra"] = {"causal-lm": f"{_P}.fetodra.modeling_fetodra:NeuronFet
 # checkpoints that name their design by ``architecture`` instead of a Hugging Face ``model_type``
 MODEL_TYPES["sodudra"] = {"causal-lm": f"{_P}.sodudra.modeling_sodudra:NeuronSodudraForCausalLM"}
 MODEL_TYPES["tusipel"] = {"causal-lm": f"{_P}.tusipel.modeling_tusipel:NeuronTusipelForCausalLM"}
-ARCHITECTURES = {"Fetodra": "fetodra", "Sodudra": "sodudra", "Tusipel": "tusipel"}
+MODEL_TYPES["zanivik"] = {"causal-lm": f"{_P}.zanivik.modeling_zanivik:NeuronZanivikForCausalLM"}
+ARCHITECTURES = {"Fetodra": "fetodra", "Sodudra": "sodudra", "Tusipel": "tusipel", "Zanivik": "zanivik"}
 TASK_TYPES = ("causal-lm", "image-text-to-text", "speech-to-text", "text-to-image", "audio-frame-classification", "audio-text-to-text")
 
 
