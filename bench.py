@@ -332,14 +332,14 @@ def main():
     ap.add_argument("--ctx", type=int, default=128)
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--skip-ci", action="store_true")
-    ap.add_argument("--config", default="llama8b", choices=["llama8b", "dbrx", "quant", "spec", "fetodra", "sodudra", "tusipel"],
+    ap.add_argument("--config", default="llama8b", choices=["llama8b", "dbrx", "quant", "spec", "fetodra", "sodudra", "tusipel", "zanivik"],
                     help="BASELINE.json config: llama8b (headline, default), dbrx (1-layer MoE), quant (Llama-2-7b fp8), "
                          "spec (open_llama 7b + 3b draft), fetodra (1 GPU: prefill / decode tokens/s of the Fetodra stack beside the Bamba "
                          "stack at equal layer sizes + per-kernel roofline table; --size picks the layer sizes), sodudra (1 GPU: the same for the "
                          "Sodudra stack beside the DeepSeek stack; --size small|large), tusipel (1 GPU: the same for the Tusipel stack beside "
-                         "the Sodudra stack; --size small|large)")
+                         "the Sodudra stack; --size small|large), zanivik (1 GPU: the same for the Zanivik stack beside the Fetodra stack; --size small|large)")
     ap.add_argument("--size", default="1b", choices=["1b", "8b", "small", "large"],
-                    help="--config fetodra: 1b | 8b (widths of a ~1B / ~8B model); --config sodudra / tusipel: small | large")
+                    help="--config fetodra: 1b | 8b (widths of a ~1B / ~8B model); --config sodudra / tusipel / zanivik: small | large")
     ap.add_argument("--prompt", type=int, default=1024, help="--config fetodra: prompt tokens per row")
     ap.add_argument("--shard-shapes", type=int, default=1,
                     help="DIAGNOSTIC (1 GPU): run the per-rank shapes of TP=N without the collectives (compute-only share of a TP step)")
@@ -347,6 +347,17 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     args.warmup = max(args.warmup, 3)
+    if args.config == "zanivik":
+        from neuronx_distributed_inference_b200.ops import _ext
+        from neuronx_distributed_inference_b200.utils.benchmark_pairs import run as run_pairs
+        _ext.load_extension()
+        sampler = ClockSampler(0)
+        sampler.start()
+        res = run_pairs(args.size if args.size in ("small", "large") else "small", args.batch if args.batch != 2 else 4, args.prompt,
+                        min(args.steps, 64), args.warmup)
+        res["clocks"] = sampler.stop()
+        print(json.dumps({"metric": "zanivik_vs_fetodra_tokens_per_sec", "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic", **res}))
+        return 0
     if args.config == "tusipel":
         from neuronx_distributed_inference_b200.ops import _ext
         from neuronx_distributed_inference_b200.utils.benchmark_conv_latent import run as run_conv_latent
